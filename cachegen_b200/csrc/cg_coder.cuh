@@ -1,0 +1,304 @@
+// The per-stream arithmetic coder: bit window, bit sink, decode loop and encode step.
+//
+// This header compiles both as CUDA device code (the product) and as plain host C++ (only so that
+// the CPU test-suite can drive exactly these loops against the oracle without a GPU; the shared
+// library never contains or calls a host build of them).
+//
+// The steps restate the reference's loops
+// (LMCache/third_party/torchac_cuda/torchac_kernel_dec_new.cu:262-302 and
+//  torchac_kernel_enc_new.cu:255-306) without the 64-bit division, the binary search on `count`
+// and the bit-serial renormalisation:
+//   * cdf[m] <= count, count = ((value-low+1)*2^16 - 1) / span, holds exactly when
+//     (span*cdf[m]) >> 16 <= value - low, so the search compares scaled table entries with
+//     value - low directly;
+//   * within one symbol the renormalisation loop does a run of "equal top bit" shifts followed
+//     by a run of "underflow" shifts, never the other way round; both run lengths come from a
+//     count-leading-zeros, the decoder's `value` takes all its new bits in one funnel shift and
+//     the encoder emits the shifted-out top bits of `low` in one append.
+#pragma once
+
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define CG_HD __host__ __device__ __forceinline__
+#else
+#define CG_HD inline
+#endif
+
+namespace cg {
+
+constexpr int kGroupChannels = 128;            // streams (threads) per coder block
+constexpr int kTableRowBytes = kGroupChannels * 4;  // bytes between table entries m and m+1 of a stream
+
+// ---- intrinsics with host stand-ins -----------------------------------------------------------------
+CG_HD int cg_clz(uint32_t x) {
+#if defined(__CUDA_ARCH__)
+    return __clz(static_cast<int>(x));
+#else
+    return x ? __builtin_clz(x) : 32;
+#endif
+}
+// upper 32 bits of (hi:lo) << (s & 31)
+CG_HD uint32_t cg_fshl(uint32_t lo, uint32_t hi, uint32_t s) {
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_l(lo, hi, s);
+#else
+    s &= 31u;
+    return s ? ((hi << s) | (lo >> (32u - s))) : hi;
+#endif
+}
+// upper 32 bits of (hi:lo) << min(s, 32)
+CG_HD uint32_t cg_fshl_clamp(uint32_t lo, uint32_t hi, uint32_t s) {
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_lc(lo, hi, s);
+#else
+    if (s >= 32u) return lo;
+    return s ? ((hi << s) | (lo >> (32u - s))) : hi;
+#endif
+}
+// lower 32 bits of (hi:lo) >> min(s, 32)
+CG_HD uint32_t cg_fshr_clamp(uint32_t lo, uint32_t hi, uint32_t s) {
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_rc(lo, hi, s);
+#else
+    if (s >= 32u) return hi;
+    return s ? ((lo >> s) | (hi << (32u - s))) : lo;
+#endif
+}
+CG_HD uint32_t cg_bswap32(uint32_t v) {
+#if defined(__CUDA_ARCH__)
+    return __byte_perm(v, 0, 0x0123);
+#else
+    return __builtin_bswap32(v);
+#endif
+}
+CG_HD uint32_t cg_load_stream_word(const uint32_t *p) {
+#if defined(__CUDA_ARCH__)
+    return __ldg(p);
+#else
+    return *p;
+#endif
+}
+
+// upper 32 bits of span * c16 where span = spanm1 + 1 (span may be 2^32) and c16 = cdf << 16:
+// equals the (span * cdf) >> 16 of the range update (enc_new.cu:262-263), without the 64-bit shift.
+CG_HD uint32_t scale_by_cdf(uint32_t spanm1, uint32_t c16) {
+    const uint64_t t = static_cast<uint64_t>(spanm1) * c16 + c16;
+    return static_cast<uint32_t>(t >> 32);
+}
+
+// Count of equal-top-bit shifts for the interval [low, high] (the |1 keeps it below 32 on a
+// degenerate interval, which only a corrupt table can produce).
+CG_HD int equal_shifts(uint32_t low, uint32_t high) { return cg_clz((low ^ high) | 1u); }
+// Count of underflow shifts once the top bits differ: the run, from bit 30 down, of positions where
+// low has a 1 and high a 0.
+CG_HD int underflow_shifts(uint32_t low, uint32_t high) { return cg_clz((((~low) | high) << 1) | 1u); }
+
+// ---- table access ---------------------------------------------------------------------------------------
+// A stream's table is the column tab[m][tid] = cdf[m] << 16 of a [rows][128] uint32 array, addressed
+// by byte address: entry m of the column starting at `col` is at col + m * kTableRowBytes.  On the
+// device the addresses are shared-memory addresses (bank = lane for every m); on the host they are
+// offsets into a plain array.
+struct TableReader {
+#if defined(__CUDA_ARCH__)
+    __device__ __forceinline__ uint32_t operator()(uint32_t addr) const {
+        uint32_t v;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+        return v;
+    }
+#else
+    const uint8_t *base;
+    uint32_t operator()(uint32_t addr) const { return *reinterpret_cast<const uint32_t *>(base + addr); }
+#endif
+};
+
+// ---- MSB-first bit window over one stream ------------------------------------------------------------
+// The byte array is read as aligned 32-bit words; bits before the stream's first byte are shifted
+// out at start-up and words (or word tails) past its last byte read as zero, which is what the
+// reference sees in its zero-padded staging row (dec_new.cu:229-232).
+struct BitWindow {
+    const uint32_t *wp;  // word holding the stream's first byte
+    uint32_t end_bit;    // bit index, counted from wp, one past the stream's last bit
+    uint32_t hi, lo;     // next unread bits, hi's top bit first
+    int nbits;           // valid bits in hi:lo
+    int next;            // next word to fetch
+
+    CG_HD uint32_t fetch(int j) const {
+        const uint32_t b0 = static_cast<uint32_t>(j) * 32u;
+        if (b0 >= end_bit) return 0u;
+        uint32_t w = cg_bswap32(cg_load_stream_word(wp + j));
+        const uint32_t rem = end_bit - b0;
+        if (rem < 32u) w &= 0xFFFFFFFFu << (32u - rem);
+        return w;
+    }
+    // returns the stream's first 32 bits (the coder's initial `value`, dec_new.cu:257)
+    CG_HD uint32_t open(const uint8_t *p, uint32_t len) {
+        const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+        wp = reinterpret_cast<const uint32_t *>(a & ~static_cast<uintptr_t>(3));
+        const uint32_t off = static_cast<uint32_t>(a & 3u) * 8u;
+        end_bit = off + len * 8u;
+        const uint32_t w0 = fetch(0), w1 = fetch(1), w2 = fetch(2);
+        const uint32_t value = cg_fshl(w1, w0, off);
+        hi = cg_fshl(w2, w1, off);
+        lo = w2 << off;
+        nbits = 64 - static_cast<int>(off);
+        next = 3;
+        return value;
+    }
+    // shifts s (< 32) fresh bits into `value`
+    CG_HD uint32_t feed(uint32_t value, int s) {
+        value = cg_fshl(hi, value, static_cast<uint32_t>(s));
+        hi = cg_fshl(lo, hi, static_cast<uint32_t>(s));
+        lo <<= s;
+        nbits -= s;
+        if (nbits <= 32) {
+            const uint32_t w = fetch(next++);
+            hi |= cg_fshr_clamp(w, 0u, static_cast<uint32_t>(nbits));
+            lo = cg_fshl_clamp(0u, w, static_cast<uint32_t>(32 - nbits));
+            nbits += 32;
+        }
+        return value;
+    }
+};
+
+// ---- decode loop ------------------------------------------------------------------------------------------
+// col: address of the stream's table column; emit(i, m) receives token index and symbol.
+// LEVELS: search depth, 2^LEVELS >= maxsym + 1.  POW2: 2^LEVELS == maxsym + 1, so no candidate can
+// exceed maxsym and the bound check is dropped.
+template <int LEVELS, bool POW2, class Emit>
+CG_HD void decode_stream(TableReader tab, uint32_t col, int maxsym, BitWindow &bw, uint32_t value, int ntok,
+                         Emit emit) {
+    uint32_t low = 0u, high = 0xFFFFFFFFu;
+    const uint32_t a_max = col + static_cast<uint32_t>(maxsym) * kTableRowBytes;
+    for (int i = 0; i < ntok; ++i) {
+        const uint32_t spanm1 = high - low;
+        const uint32_t target = value - low;
+        // largest m in [0, maxsym] with (span*cdf[m]) >> 16 <= target (binsearch, dec_new.cu:52-71)
+        uint32_t a = col;
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+        for (int b = LEVELS - 1; b >= 0; --b) {
+            const uint32_t ca = a + (static_cast<uint32_t>(kTableRowBytes) << b);
+            const uint32_t f = scale_by_cdf(spanm1, tab(ca));
+            bool take = f <= target;
+            if (!POW2) take = take && (ca <= a_max);
+            a = take ? ca : a;
+        }
+        emit(i, static_cast<int>((a - col) / kTableRowBytes));
+        if (i == ntok - 1) break;  // no range update after the last symbol (dec_new.cu:273-275)
+
+        const uint32_t flo = scale_by_cdf(spanm1, tab(a));
+        const uint32_t fhi = (a == a_max) ? spanm1 + 1u : scale_by_cdf(spanm1, tab(a + kTableRowBytes));
+        high = low + fhi - 1u;
+        low = low + flo;
+        // equal-top-bit shifts, then underflow shifts (dec_new.cu:283-301)
+        const int n1 = equal_shifts(low, high);
+        low <<= n1;
+        high = cg_fshl(0xFFFFFFFFu, high, static_cast<uint32_t>(n1));
+        const int k = underflow_shifts(low, high);
+        low = (low << k) & 0x7FFFFFFFu;
+        high = cg_fshl(0xFFFFFFFFu, high, static_cast<uint32_t>(k)) | 0x80000000u;
+        // k underflow steps of "value -= 2^30; value = value*2 + bit" flip only the top bit of the
+        // shifted value
+        value = bw.feed(value, (n1 + k) & 31);
+        value ^= (k != 0) ? 0x80000000u : 0u;
+    }
+}
+
+// ---- MSB-first bit writer into one scratch row (add_bits_to_output, enc_new.cu:21-97) ---------------------
+struct BitSink {
+    uint32_t *row;    // 4-byte aligned scratch row of this stream
+    uint32_t cap_w;   // words that fit in the row
+    uint32_t nwords;  // words produced so far (may exceed cap_w: then nothing more is stored)
+    uint64_t acc;     // pending output bits, right-aligned
+    int nacc;         // number of bits in acc, < 32 between calls
+
+    CG_HD void init(uint8_t *p, int64_t stride) {
+        row = reinterpret_cast<uint32_t *>(p);
+        cap_w = static_cast<uint32_t>(stride >> 2);
+        nwords = 0;
+        acc = 0;
+        nacc = 0;
+    }
+    // appends the low n (0..32) bits of v (v has no bits above n)
+    CG_HD void put(uint32_t v, int n) {
+        acc = (acc << n) | v;
+        nacc += n;
+        if (nacc >= 32) {
+            nacc -= 32;
+            const uint32_t w = static_cast<uint32_t>(acc >> nacc);
+            if (nwords < cap_w) row[nwords] = cg_bswap32(w);
+            nwords++;
+        }
+    }
+    // `count` copies of `bit`
+    CG_HD void put_run(uint32_t bit, uint32_t count) {
+        const uint32_t ones = 0u - bit;  // 0 or 0xFFFFFFFF
+        while (count >= 32u) {
+            put(ones, 32);
+            count -= 32u;
+        }
+        if (count) put(ones >> (32u - count), static_cast<int>(count));
+    }
+    // zero-fills to a byte boundary; returns the stream length in bytes
+    CG_HD uint32_t finish() {
+        const uint32_t bytes = nwords * 4u + static_cast<uint32_t>((nacc + 7) >> 3);
+        if (nacc) {
+            const uint32_t w = static_cast<uint32_t>(acc << (32 - nacc));
+            if (nwords < cap_w) row[nwords] = cg_bswap32(w);
+        }
+        return bytes;
+    }
+};
+
+// ---- encoder state and step -----------------------------------------------------------------------------
+struct EncoderState {
+    uint32_t low, high, pending;
+    CG_HD void init() {
+        low = 0u;
+        high = 0xFFFFFFFFu;
+        pending = 0u;
+    }
+    // one symbol s in [0, maxsym] (enc_new.cu:257-295)
+    CG_HD void step(TableReader tab, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out) {
+        const uint32_t a = col + s * kTableRowBytes;
+        const uint32_t spanm1 = high - low;
+        const uint32_t flo = scale_by_cdf(spanm1, tab(a));
+        const uint32_t fhi = (s == maxsym) ? spanm1 + 1u : scale_by_cdf(spanm1, tab(a + kTableRowBytes));
+        high = low + fhi - 1u;
+        low = low + flo;
+        // equal-top-bit shifts: their n1 bits are low's top bits; the first is followed by the pending
+        // (inverted) bits of earlier underflow shifts (enc_new.cu:275-287)
+        const int n1 = equal_shifts(low, high);
+        if (n1) {
+            const uint32_t bits = low >> (32 - n1);
+            if (pending == 0u) {
+                out.put(bits, n1);
+            } else {
+                const uint32_t first = bits >> (n1 - 1);
+                out.put(first, 1);
+                out.put_run(1u - first, pending);
+                out.put(bits & ((1u << (n1 - 1)) - 1u), n1 - 1);
+                pending = 0u;
+            }
+            low <<= n1;
+            high = cg_fshl(0xFFFFFFFFu, high, static_cast<uint32_t>(n1));
+        }
+        // underflow shifts (enc_new.cu:288-293)
+        const int k = underflow_shifts(low, high);
+        pending += static_cast<uint32_t>(k);
+        low = (low << k) & 0x7FFFFFFFu;
+        high = cg_fshl(0xFFFFFFFFu, high, static_cast<uint32_t>(k)) | 0x80000000u;
+    }
+    // final flush (enc_new.cu:298-306); returns the stream length in bytes
+    CG_HD uint32_t flush(BitSink &out) {
+        pending += 1u;
+        const uint32_t last = (low < 0x40000000u) ? 0u : 1u;
+        out.put(last, 1);
+        out.put_run(1u - last, pending);
+        return out.finish();
+    }
+};
+
+}  // namespace cg

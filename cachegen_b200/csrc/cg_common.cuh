@@ -1,0 +1,95 @@
+// Shared device helpers of the sm_100a CacheGen codec kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/cachegen_b200.h"
+#include "cg_coder.cuh"
+
+namespace cg {
+
+constexpr int kGroup = kGroupChannels;           // streams (threads) per coder block
+constexpr int kRowBytes = kTableRowBytes;        // bytes of one table row in shared memory
+static_assert(kGroup == CG_GROUP_CHANNELS, "header and kernels disagree on the group size");
+constexpr int kSubTokens = CG_MAX_TOKENS_PER_STREAM;
+
+// ---- error plumbing -------------------------------------------------------------------------
+int set_cuda_error(cudaError_t e);  // records the text, returns CG_E_CUDA
+inline int check_launch() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? CG_OK : set_cuda_error(e);
+}
+
+// ---- search depth for a table of lp entries ---------------------------------------------------
+// Symbols are 0 .. lp-2.  levels = smallest n with 2^n >= lp-1; pow2 when 2^n == lp-1.
+inline int search_levels(int lp) {
+    int n = 0;
+    while ((1 << n) < lp - 1) n++;
+    return n;
+}
+
+// ---- small PTX wrappers -----------------------------------------------------------------------
+__device__ __forceinline__ float ldsf32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- table staging ----------------------------------------------------------------------------
+// Every thread owns one (row, channel) table.  It is kept in shared memory as tab[m][tid] =
+// cdf[m] << 16 so that lane i always hits bank i, whatever entry m each lane is at.  Each thread
+// fills (and later reads) only its own column, so no block barrier is needed.
+__device__ __forceinline__ void stage_table_column(uint32_t *tab, const int16_t *cdf_row, int lp,
+                                                   int rows, int tid) {
+    for (int m = 0; m < lp; ++m)
+        tab[m * kGroup + tid] = static_cast<uint32_t>(static_cast<uint16_t>(__ldg(cdf_row + m))) << 16;
+    for (int m = lp; m < rows; ++m) tab[m * kGroup + tid] = 0u;
+}
+
+// ---- block-wide exclusive scan over kGroup (=128) ints ------------------------------------------
+// warp_sums: shared int[4].  Returns the exclusive prefix of `v` across the block.
+__device__ __forceinline__ int block_exclusive_scan_128(int v, int *warp_sums, int tid, int *total) {
+    const int lane = tid & 31, w = tid >> 5;
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        int n = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+        if (lane >= d) incl += n;
+    }
+    if (lane == 31) warp_sums[w] = incl;
+    __syncthreads();
+    int base = 0, all = 0;
+#pragma unroll
+    for (int i = 0; i < kGroup / 32; ++i) {
+        const int s = warp_sums[i];
+        if (i < w) base += s;
+        all += s;
+    }
+    if (total) *total = all;
+    return base + incl - v;
+}
+
+template <int DT> struct Half16;
+template <> struct Half16<CG_F16> {
+    static __device__ __forceinline__ float to_float(uint16_t b) { return __half2float(__ushort_as_half(b)); }
+    static __device__ __forceinline__ uint16_t from_float(float f) { return __half_as_ushort(__float2half_rn(f)); }
+};
+template <> struct Half16<CG_BF16> {
+    static __device__ __forceinline__ float to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+    static __device__ __forceinline__ uint16_t from_float(float f) { return __bfloat16_as_ushort(__float2bfloat16_rn(f)); }
+};
+
+__device__ __forceinline__ float half_bits_to_float(uint16_t b, int dtype) {
+    return dtype == CG_BF16 ? Half16<CG_BF16>::to_float(b) : Half16<CG_F16>::to_float(b);
+}
+
+// Cq of do_dequantize / MAX of torch_quant_vectorized: bins // 2 - 1 on a float tensor.
+__device__ __forceinline__ float half_range(float bins) { return __fsub_rn(floorf(__fdiv_rn(bins, 2.0f)), 1.0f); }
+
+}  // namespace cg

@@ -1,0 +1,240 @@
+// Arithmetic decoder kernels: one thread per stream, 128 adjacent channels of one row per block.
+//
+// The per-stream loop lives in cg_coder.cuh; this file stages tables, offsets and scales around it
+// and writes either raw symbols (the torchac_cuda entry points) or dequantised 16-bit KV (fused path).
+#include "cg_common.cuh"
+
+namespace cg {
+
+// ---- symbol-output kernels (decode_fast_prefsum / decode_fast_new) -----------------------------------
+struct SymDecodeParams {
+    const int16_t *cdf;
+    const uint8_t *bytes;
+    int64_t nbytes;          // total bytes addressable from `bytes`
+    const int64_t *prefsum;  // mode 0
+    const int32_t *lengths;  // mode 1
+    int64_t stream_stride;   // mode 1
+    uint8_t *out;
+    int64_t o0, o1, o2;
+    int ntokens, nchannels, lp;
+    int32_t *status;
+};
+
+template <int LEVELS, bool POW2, int MODE>
+__global__ void __launch_bounds__(kGroup) decode_symbols_kernel(const SymDecodeParams p) {
+    extern __shared__ uint32_t tab[];
+    const int tid = threadIdx.x;
+    const int row = blockIdx.y;
+    const int c = blockIdx.x * kGroup + tid;
+    if (c >= p.nchannels) return;  // no block barrier in this kernel
+    const int64_t g = static_cast<int64_t>(row) * p.nchannels + c;
+    int64_t start, len;
+    if (MODE == 0) {
+        start = g ? p.prefsum[g - 1] : 0;
+        len = p.prefsum[g] - start;
+    } else {
+        start = g * p.stream_stride;
+        len = p.lengths[g];
+        if (len > p.stream_stride) len = p.stream_stride;
+    }
+    bool bad = false;
+    if (len < 0) { len = 0; bad = true; }
+    if (start < 0) { start = 0; len = 0; bad = true; }
+    if (start > p.nbytes) { start = p.nbytes; bad = true; }
+    if (start + len > p.nbytes) { len = p.nbytes - start; bad = true; }
+    if (len > (1 << 20)) len = 1 << 20;
+    if (bad && p.status) atomicOr(p.status, CG_S_BAD_LENGTHS);
+
+    const int rows = (1 << LEVELS) > p.lp ? (1 << LEVELS) : p.lp;
+    stage_table_column(tab, p.cdf + g * p.lp, p.lp, rows, tid);
+    BitWindow bw;
+    const uint32_t value = bw.open(p.bytes + start, static_cast<uint32_t>(len));
+    uint8_t *o = p.out + row * p.o0 + c * p.o2;
+    const int64_t o1 = p.o1;
+    decode_stream<LEVELS, POW2>(TableReader{}, smem_addr(tab + tid), p.lp - 2, bw, value, p.ntokens,
+                                [&](int i, int m) { o[i * o1] = static_cast<uint8_t>(m); });
+}
+
+// ---- fused decode + dequantise + KV-layout store --------------------------------------------------------
+struct FusedDecodeParams {
+    int njobs, nlayers, nheads, head_size, nchannels, lp, nslab;
+    const float *bins;
+    int64_t o_layer, o_kv, o_token, o_head;
+    int32_t *status;
+    cg_decode_job jobs[CG_MAX_DECODE_JOBS];
+};
+
+template <int LEVELS, bool POW2, int SCALE_DT, int OUT_DT>
+__global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_constant__ FusedDecodeParams p) {
+    extern __shared__ uint32_t smem[];
+    __shared__ float scale_f[kSubTokens];
+    __shared__ float lut[CG_MAX_LP];
+    __shared__ int warp_sums[kGroup / 32];
+
+    const cg_decode_job &job = p.jobs[blockIdx.z];
+    const int tid = threadIdx.x;
+    const int row = blockIdx.y;
+    const int c = blockIdx.x * kGroup + tid;
+    const bool active = c < p.nchannels;
+    const int ntok = job.ntokens;
+    const int layer = row % p.nlayers, kv = row / p.nlayers;
+    const int64_t g = static_cast<int64_t>(row) * p.nchannels + c;
+
+    // stream offsets: group base + exclusive scan of this block's lengths (cachegen_decoder.py:70)
+    int len = active ? __ldg(job.lengths + g) : 0;
+    bool bad = false;
+    if (len < 0) { len = 0; bad = true; }
+    if (len > (1 << 20)) { len = 1 << 20; bad = true; }
+    const int excl = block_exclusive_scan_128(len, warp_sums, tid, nullptr);
+    int64_t start = __ldg(job.group_off + static_cast<int64_t>(row) * p.nslab + blockIdx.x) + excl;
+    if (start > job.nbytes) { start = job.nbytes; bad = true; }
+    if (start + len > job.nbytes) { len = static_cast<int>(job.nbytes - start); bad = true; }
+    if (bad && active && p.status) atomicOr(p.status, CG_S_BAD_LENGTHS);
+
+    // per-token scales of this row and the row's (s - Cq) / Cq table (cachegen_decoder.py:30-32)
+    const uint16_t *sc = static_cast<const uint16_t *>(kv ? job.scales_v : job.scales_k) +
+                         static_cast<int64_t>(layer) * job.scale_stride;
+    for (int t = tid; t < ntok; t += kGroup) scale_f[t] = Half16<SCALE_DT>::to_float(__ldg(sc + t));
+    if (tid < p.lp - 1) {
+        const float cq = half_range(__ldg(p.bins + row));
+        lut[tid] = __fdiv_rn(__fsub_rn(static_cast<float>(tid), cq), cq);
+    }
+    const int rows = (1 << LEVELS) > p.lp ? (1 << LEVELS) : p.lp;
+    if (active) stage_table_column(smem, job.cdf + g * p.lp, p.lp, rows, tid);
+    __syncthreads();
+    if (!active) return;
+
+    BitWindow bw;
+    const uint32_t value = bw.open(job.bytes + start, static_cast<uint32_t>(len));
+    const int h = c / p.head_size, d = c - h * p.head_size;
+    uint16_t *o = static_cast<uint16_t *>(job.out) + layer * p.o_layer + kv * p.o_kv + h * p.o_head + d;
+    const int64_t o_token = p.o_token;
+    const uint32_t lut_a = smem_addr(lut), sc_a = smem_addr(scale_f);
+    decode_stream<LEVELS, POW2>(TableReader{}, smem_addr(smem + tid), p.lp - 2, bw, value, ntok, [&](int i, int m) {
+        // ((sym - Cq) / Cq) * max in fp32, then one round-to-nearest cast (cachegen_decoder.py:30-33,171-173)
+        const float v = __fmul_rn(ldsf32(lut_a + 4u * m), ldsf32(sc_a + 4u * i));
+        o[i * o_token] = Half16<OUT_DT>::from_float(v);
+    });
+}
+
+// ---- launch helpers -------------------------------------------------------------------------------------
+static size_t table_bytes(int lp, int levels) {
+    const int rows = (1 << levels) > lp ? (1 << levels) : lp;
+    return static_cast<size_t>(rows) * kRowBytes;
+}
+
+// Instantiated search depths: exact power-of-two tables for lp = 9, 17, 33 and clamped searches of
+// depth 3..6 for every other lp <= 64.
+template <int MODE>
+static int launch_symbols(const SymDecodeParams &p, int nrows, cudaStream_t st) {
+    const int need = search_levels(p.lp);
+    const bool pow2 = (1 << need) == p.lp - 1;
+    const dim3 grid((p.nchannels + kGroup - 1) / kGroup, nrows), block(kGroup);
+#define CG_LAUNCH_SYM(L, P2) \
+    decode_symbols_kernel<L, P2, MODE><<<grid, block, table_bytes(p.lp, L), st>>>(p)
+    if (pow2 && need == 5) CG_LAUNCH_SYM(5, true);
+    else if (pow2 && need == 4) CG_LAUNCH_SYM(4, true);
+    else if (pow2 && need == 3) CG_LAUNCH_SYM(3, true);
+    else if (need <= 3) CG_LAUNCH_SYM(3, false);
+    else if (need == 4) CG_LAUNCH_SYM(4, false);
+    else if (need == 5) CG_LAUNCH_SYM(5, false);
+    else CG_LAUNCH_SYM(6, false);
+#undef CG_LAUNCH_SYM
+    return check_launch();
+}
+
+template <int SCALE_DT, int OUT_DT>
+static int launch_fused(const FusedDecodeParams &p, cudaStream_t st) {
+    const int need = search_levels(p.lp);
+    const bool pow2 = (1 << need) == p.lp - 1;
+    const dim3 grid(p.nslab, 2 * p.nlayers, p.njobs), block(kGroup);
+#define CG_LAUNCH_FUSED(L, P2) \
+    decode_dequant_kernel<L, P2, SCALE_DT, OUT_DT><<<grid, block, table_bytes(p.lp, L), st>>>(p)
+    if (pow2 && need == 5) CG_LAUNCH_FUSED(5, true);
+    else if (pow2 && need == 4) CG_LAUNCH_FUSED(4, true);
+    else if (pow2 && need == 3) CG_LAUNCH_FUSED(3, true);
+    else if (need <= 3) CG_LAUNCH_FUSED(3, false);
+    else if (need == 4) CG_LAUNCH_FUSED(4, false);
+    else if (need == 5) CG_LAUNCH_FUSED(5, false);
+    else CG_LAUNCH_FUSED(6, false);
+#undef CG_LAUNCH_FUSED
+    return check_launch();
+}
+
+}  // namespace cg
+
+using namespace cg;
+
+static int check_coder_shape(int nrows, int ntokens, int nchannels, int lp) {
+    if (nrows <= 0 || ntokens <= 0 || nchannels <= 0) return CG_E_SHAPE;
+    if (ntokens > CG_MAX_TOKENS_PER_STREAM) return CG_E_TOKENS;
+    if (lp < 2 || lp > CG_MAX_LP) return CG_E_LP;
+    if (nrows > 65535) return CG_E_SHAPE;
+    return CG_OK;
+}
+
+extern "C" int cg_decode_prefsum(const int16_t *cdf, const uint8_t *bytes, int64_t nbytes,
+                                 const int64_t *prefsum, uint8_t *out, const int64_t out_strides[3],
+                                 int nrows, int ntokens, int nchannels, int lp, int32_t *status,
+                                 void *stream) {
+    if (!cdf || !prefsum || !out || !out_strides || (!bytes && nbytes > 0)) return CG_E_NULL;
+    if (nbytes < 0) return CG_E_SHAPE;
+    if (int rc = check_coder_shape(nrows, ntokens, nchannels, lp)) return rc;
+    SymDecodeParams p{cdf, bytes, nbytes, prefsum, nullptr, 0, out, out_strides[0], out_strides[1],
+                      out_strides[2], ntokens, nchannels, lp, status};
+    return launch_symbols<0>(p, nrows, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cg_decode_padded(const int16_t *cdf, const uint8_t *streams, int64_t stream_stride,
+                                const int32_t *lengths, uint8_t *out, const int64_t out_strides[3],
+                                int nrows, int ntokens, int nchannels, int lp, int32_t *status,
+                                void *stream) {
+    if (!cdf || !streams || !lengths || !out || !out_strides) return CG_E_NULL;
+    if (stream_stride <= 0) return CG_E_SHAPE;
+    if (int rc = check_coder_shape(nrows, ntokens, nchannels, lp)) return rc;
+    SymDecodeParams p{cdf, streams, static_cast<int64_t>(nrows) * nchannels * stream_stride, nullptr,
+                      lengths, stream_stride, out, out_strides[0], out_strides[1], out_strides[2],
+                      ntokens, nchannels, lp, status};
+    return launch_symbols<1>(p, nrows, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int nlayers, int nheads,
+                                 int head_size, int lp, const float *bins, int scale_dtype,
+                                 int out_dtype, int64_t o_layer, int64_t o_kv, int64_t o_token,
+                                 int64_t o_head, int32_t *status, void *stream) {
+    if (!jobs_host || !bins) return CG_E_NULL;
+    if (njobs <= 0 || nlayers <= 0 || nheads <= 0 || head_size <= 0) return CG_E_SHAPE;
+    if (njobs > CG_MAX_DECODE_JOBS) return CG_E_CAPACITY;
+    if (lp < 2 || lp > CG_MAX_LP) return CG_E_LP;
+    if (2 * nlayers > 65535) return CG_E_SHAPE;
+    if ((scale_dtype != CG_F16 && scale_dtype != CG_BF16) || (out_dtype != CG_F16 && out_dtype != CG_BF16))
+        return CG_E_DTYPE;
+    FusedDecodeParams p;
+    p.njobs = njobs;
+    p.nlayers = nlayers;
+    p.nheads = nheads;
+    p.head_size = head_size;
+    p.nchannels = nheads * head_size;
+    p.lp = lp;
+    p.nslab = (p.nchannels + kGroup - 1) / kGroup;
+    p.bins = bins;
+    p.o_layer = o_layer;
+    p.o_kv = o_kv;
+    p.o_token = o_token;
+    p.o_head = o_head;
+    p.status = status;
+    for (int j = 0; j < njobs; ++j) {
+        const cg_decode_job &jb = jobs_host[j];
+        if (!jb.cdf || !jb.lengths || !jb.group_off || !jb.scales_k || !jb.scales_v || !jb.out ||
+            (!jb.bytes && jb.nbytes > 0))
+            return CG_E_NULL;
+        if (jb.ntokens <= 0 || jb.nbytes < 0) return CG_E_SHAPE;
+        if (jb.ntokens > CG_MAX_TOKENS_PER_STREAM) return CG_E_TOKENS;
+        p.jobs[j] = jb;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (scale_dtype == CG_F16 && out_dtype == CG_F16) return launch_fused<CG_F16, CG_F16>(p, st);
+    if (scale_dtype == CG_F16 && out_dtype == CG_BF16) return launch_fused<CG_F16, CG_BF16>(p, st);
+    if (scale_dtype == CG_BF16 && out_dtype == CG_F16) return launch_fused<CG_BF16, CG_F16>(p, st);
+    return launch_fused<CG_BF16, CG_BF16>(p, st);
+}

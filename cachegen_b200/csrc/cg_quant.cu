@@ -1,0 +1,250 @@
+// Quantisation, histogram and CDF-table kernels.
+//
+//  * row_absmax_kernel      : per (row, token) amax(|x|) over all channels, the scale of
+//                             torch_quant_vectorized (cachegen_encoder.py:55 in the reference);
+//  * quantize_cdf_kernel    : per (row, 128-channel slab): quantise every token of the chunk with
+//                             128-bit loads, write int8 symbols, count them with shared-memory
+//                             atomics, and turn the counts into the reference's int16 tables
+//                             (cachegen_encoder.py:54-57, cal_cdf.cu:29-49);
+//  * symbol_cdf_kernel      : the stand-alone calculate_cdf on int8 symbols (cal_cdf.cu:17-59).
+#include "cg_common.cuh"
+
+namespace cg {
+
+struct KvLayout {
+    int64_t s_layer, s_kv, s_token, s_head;
+    int nlayers, ntokens, nheads, head_size;
+};
+
+// |x| as an ordered integer: 16-bit float magnitudes compare like their bit patterns
+__device__ __forceinline__ uint32_t absmax2(uint32_t best, uint32_t packed) {
+    return __vmaxu2(best, packed & 0x7FFF7FFFu);
+}
+
+// One warp per (row, token).  scales[row, token] gets the 16-bit pattern of max|x|.
+template <int VEC>
+__global__ void __launch_bounds__(256) row_absmax_kernel(const uint16_t *__restrict__ kv, const KvLayout L,
+                                                         uint16_t *__restrict__ scales) {
+    const int64_t wid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    const int nrows = 2 * L.nlayers;
+    if (wid >= static_cast<int64_t>(nrows) * L.ntokens) return;
+    const int row = static_cast<int>(wid / L.ntokens), t = static_cast<int>(wid % L.ntokens);
+    const int layer = row % L.nlayers, j = row / L.nlayers;
+    const uint16_t *base = kv + layer * L.s_layer + j * L.s_kv + t * L.s_token;
+    uint32_t best = 0;
+    if (VEC == 8) {
+        const int per_head = L.head_size / 8;
+        const int nvec = L.nheads * per_head;
+        for (int v = lane; v < nvec; v += 32) {
+            const int h = v / per_head, d = (v - h * per_head) * 8;
+            const uint4 q = __ldg(reinterpret_cast<const uint4 *>(base + h * L.s_head + d));
+            best = absmax2(absmax2(absmax2(absmax2(best, q.x), q.y), q.z), q.w);
+        }
+    } else {
+        const int C = L.nheads * L.head_size;
+        for (int c = lane; c < C; c += 32) {
+            const int h = c / L.head_size, d = c - h * L.head_size;
+            best = absmax2(best, __ldg(base + h * L.s_head + d));
+        }
+    }
+    best = max(best & 0xFFFFu, best >> 16);
+#pragma unroll
+    for (int d = 16; d; d >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, d));
+    if (lane == 0) scales[wid] = static_cast<uint16_t>(best);
+}
+
+// Counts to table (normalize_cdf_value, cal_cdf.cu:11-15,40-49), one thread per channel.
+// hist: shared uint32 [max_bins+1][kGroup], hist[v+1][c] = #{sym == v}.  Writes the channel's
+// lp = max_bins+1 entries to out16 (shared uint16 [kGroup][lp]).
+__device__ __forceinline__ void counts_to_table(const uint32_t *hist, int max_bins, int cl, uint16_t *out16) {
+    const int lp = max_bins + 1;
+    uint32_t total = 0;
+    for (int i = 1; i <= max_bins; ++i) total += hist[i * kGroup + cl];
+    total &= 0xFFFFu;  // the reference accumulates in uint16
+    const uint32_t scale = 0xFFFFu - static_cast<uint32_t>(max_bins);
+    uint32_t cum = 0;
+    for (int i = 0; i <= max_bins; ++i) {
+        if (i) cum = (cum + hist[i * kGroup + cl]) & 0xFFFFu;
+        const uint32_t nv = total ? (scale * cum / total) : 0u;
+        out16[cl * lp + i] = static_cast<uint16_t>(nv + i);
+    }
+}
+
+__device__ __forceinline__ void store_tables(const uint16_t *out16, int16_t *cdf_out, int64_t row, int c0,
+                                             int nchannels, int lp, int tid, int nthreads) {
+    // the block's tables are one contiguous run of the output
+    const int nch = min(kGroup, nchannels - c0);
+    uint16_t *dst = reinterpret_cast<uint16_t *>(cdf_out) + (row * nchannels + c0) * lp;
+    const int n = nch * lp;
+    if (((reinterpret_cast<uintptr_t>(dst) & 3) == 0) && ((n & 1) == 0)) {
+        const uint32_t *s32 = reinterpret_cast<const uint32_t *>(out16);
+        uint32_t *d32 = reinterpret_cast<uint32_t *>(dst);
+        for (int i = tid; i < n / 2; i += nthreads) d32[i] = s32[i];
+    } else {
+        for (int i = tid; i < n; i += nthreads) dst[i] = out16[i];
+    }
+}
+
+constexpr int kQuantThreads = 256;
+
+// grid (nslab, nrows).  VEC = 8: every thread quantises 8 adjacent channels of one token per step
+// (one 128-bit load, one 64-bit symbol store); VEC = 1: scalar fallback for odd shapes.
+template <int DT, int VEC>
+__global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
+    const uint16_t *__restrict__ kv, const KvLayout L, const float *__restrict__ bins,
+    const uint16_t *__restrict__ scales, int max_bins, int8_t *__restrict__ sym_out,
+    int16_t *__restrict__ cdf_out) {
+    extern __shared__ uint32_t hist[];  // [max_bins+1][kGroup], then uint16 tables [kGroup][lp]
+    const int lp = max_bins + 1;
+    uint16_t *out16 = reinterpret_cast<uint16_t *>(hist + lp * kGroup);
+    const int tid = threadIdx.x;
+    const int row = blockIdx.y, c0 = blockIdx.x * kGroup;
+    const int C = L.nheads * L.head_size, T = L.ntokens;
+    const int layer = row % L.nlayers, j = row / L.nlayers;
+    for (int i = tid; i < lp * kGroup; i += kQuantThreads) hist[i] = 0u;
+    __syncthreads();
+
+    const float MAX = half_range(__ldg(bins + row));
+    const uint16_t *base = kv + layer * L.s_layer + j * L.s_kv;
+    const uint16_t *srow = scales + static_cast<int64_t>(row) * T;
+    int8_t *orow = sym_out + static_cast<int64_t>(row) * T * C;
+
+    if (VEC == 8) {
+        constexpr int kLanesPerToken = kGroup / 8;                     // 16
+        constexpr int kTokensPerStep = kQuantThreads / kLanesPerToken;  // 16
+        const int q = tid % kLanesPerToken, tsub = tid / kLanesPerToken;
+        const int c = c0 + q * 8;
+        const int h = c / L.head_size, d = c - h * L.head_size;
+        // lanes q, q+4, q+8, q+12 of a token (and the second token of the warp) start their
+        // histogram updates at different channels, so that the 32 lanes of a warp always hit 32
+        // different banks of hist[.][channel]
+        const int rot = (threadIdx.x & 31) >> 2;
+        if (c < C) {
+            for (int t = tsub; t < T; t += kTokensPerStep) {
+                const uint16_t mbits = __ldg(srow + t);
+                const float factor = __fdiv_rn(MAX, Half16<DT>::to_float(mbits));
+                const uint32_t keep = mbits ? 0xFFu : 0u;  // all-zero token: 0 * inf = NaN -> symbol 0
+                const uint4 x = __ldg(reinterpret_cast<const uint4 *>(base + t * L.s_token + h * L.s_head + d));
+                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+                uint64_t packed = 0;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const uint16_t hb = static_cast<uint16_t>(w[e >> 1] >> ((e & 1) * 16));
+                    // three separately rounded fp32 operations, then round-half-even (enc.py:56-57)
+                    const float p = __fmul_rn(Half16<DT>::to_float(hb), factor);
+                    const float qv = __fadd_rn(p, MAX);
+                    const uint32_t s = __float_as_uint(__fadd_rn(qv, 8388608.0f)) & keep;
+                    packed |= static_cast<uint64_t>(s) << (8 * e);
+                }
+                *reinterpret_cast<uint64_t *>(orow + static_cast<int64_t>(t) * C + c) = packed;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int ee = (e + rot) & 7;
+                    const uint32_t s = static_cast<uint32_t>(packed >> (8 * ee)) & 0xFFu;
+                    if (s < static_cast<uint32_t>(max_bins)) atomicAdd(&hist[(s + 1) * kGroup + q * 8 + ee], 1u);
+                }
+            }
+        }
+    } else {
+        const int cl = tid % kGroup, tsub = tid / kGroup;
+        const int c = c0 + cl;
+        const int h = c / L.head_size, d = c - h * L.head_size;
+        if (c < C) {
+            for (int t = tsub; t < T; t += kQuantThreads / kGroup) {
+                const uint16_t mbits = __ldg(srow + t);
+                const float factor = __fdiv_rn(MAX, Half16<DT>::to_float(mbits));
+                const uint16_t hb = __ldg(base + t * L.s_token + h * L.s_head + d);
+                const float p = __fmul_rn(Half16<DT>::to_float(hb), factor);
+                const float qv = __fadd_rn(p, MAX);
+                const uint32_t s = mbits ? (__float_as_uint(__fadd_rn(qv, 8388608.0f)) & 0xFFu) : 0u;
+                orow[static_cast<int64_t>(t) * C + c] = static_cast<int8_t>(s);
+                if (s < static_cast<uint32_t>(max_bins)) atomicAdd(&hist[(s + 1) * kGroup + cl], 1u);
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < kGroup && c0 + tid < C) counts_to_table(hist, max_bins, tid, out16);
+    __syncthreads();
+    store_tables(out16, cdf_out, row, c0, C, lp, tid, kQuantThreads);
+}
+
+// calculate_cdf on int8 symbols with arbitrary strides: grid (nslab, nrows), 256 threads, thread
+// (channel = tid % 128, token parity = tid / 128).
+__global__ void __launch_bounds__(kQuantThreads) symbol_cdf_kernel(const int8_t *__restrict__ sym, int64_t s0,
+                                                                   int64_t s1, int64_t s2, int ntokens,
+                                                                   int nchannels, int max_bins,
+                                                                   int16_t *__restrict__ cdf_out) {
+    extern __shared__ uint32_t hist[];
+    const int lp = max_bins + 1;
+    uint16_t *out16 = reinterpret_cast<uint16_t *>(hist + lp * kGroup);
+    const int tid = threadIdx.x, cl = tid % kGroup, tsub = tid / kGroup;
+    const int row = blockIdx.y, c0 = blockIdx.x * kGroup, c = c0 + cl;
+    for (int i = tid; i < lp * kGroup; i += kQuantThreads) hist[i] = 0u;
+    __syncthreads();
+    if (c < nchannels) {
+        const int8_t *p = sym + row * s0 + c * s2;
+        for (int t = tsub; t < ntokens; t += kQuantThreads / kGroup) {
+            const uint32_t s = static_cast<uint8_t>(__ldg(p + t * s1));
+            if (s < static_cast<uint32_t>(max_bins)) atomicAdd(&hist[(s + 1) * kGroup + cl], 1u);
+        }
+    }
+    __syncthreads();
+    if (tid < kGroup && c < nchannels) counts_to_table(hist, max_bins, tid, out16);
+    __syncthreads();
+    store_tables(out16, cdf_out, row, c0, nchannels, lp, tid, kQuantThreads);
+}
+
+static size_t hist_smem_bytes(int max_bins) {
+    const int lp = max_bins + 1;
+    return static_cast<size_t>(lp) * kGroup * 4 + static_cast<size_t>(lp) * kGroup * 2;
+}
+
+}  // namespace cg
+
+using namespace cg;
+
+extern "C" int cg_calculate_cdf(const int8_t *sym, const int64_t sym_strides[3], int nrows, int ntokens,
+                                int nchannels, int max_bins, int16_t *cdf_out, void *stream) {
+    if (!sym || !sym_strides || !cdf_out) return CG_E_NULL;
+    if (nrows <= 0 || ntokens <= 0 || nchannels <= 0 || nrows > 65535) return CG_E_SHAPE;
+    if (max_bins < 1 || max_bins >= CG_MAX_LP) return CG_E_LP;
+    if (ntokens >= 65536) return CG_E_HIST;
+    const dim3 grid((nchannels + kGroup - 1) / kGroup, nrows);
+    symbol_cdf_kernel<<<grid, kQuantThreads, hist_smem_bytes(max_bins), static_cast<cudaStream_t>(stream)>>>(
+        sym, sym_strides[0], sym_strides[1], sym_strides[2], ntokens, nchannels, max_bins, cdf_out);
+    return check_launch();
+}
+
+extern "C" int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
+                               int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
+                               const float *bins, int max_bins, int8_t *sym_out, void *scales_out,
+                               int16_t *cdf_out, void *stream) {
+    if (!kv || !bins || !sym_out || !scales_out || !cdf_out) return CG_E_NULL;
+    if (nlayers <= 0 || ntokens <= 0 || nheads <= 0 || head_size <= 0 || 2 * nlayers > 65535) return CG_E_SHAPE;
+    if (max_bins < 1 || max_bins >= CG_MAX_LP) return CG_E_LP;
+    if (ntokens >= 65536) return CG_E_HIST;
+    if (dtype != CG_F16 && dtype != CG_BF16) return CG_E_DTYPE;
+    const KvLayout L{s_layer, s_kv, s_token, s_head, nlayers, ntokens, nheads, head_size};
+    const int C = nheads * head_size, nrows = 2 * nlayers;
+    // the 128-bit path needs 8-channel runs that stay inside one head and 16-byte aligned rows
+    const bool vec = (head_size % 8 == 0) && ((reinterpret_cast<uintptr_t>(kv) & 15) == 0) &&
+                     (s_layer % 8 == 0) && (s_kv % 8 == 0) && (s_token % 8 == 0) && (s_head % 8 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(sym_out) & 7) == 0);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint16_t *x = static_cast<const uint16_t *>(kv);
+    uint16_t *sc = static_cast<uint16_t *>(scales_out);
+    const int64_t nwarps = static_cast<int64_t>(nrows) * ntokens;
+    const unsigned ablocks = static_cast<unsigned>((nwarps * 32 + 255) / 256);
+    if (vec) row_absmax_kernel<8><<<ablocks, 256, 0, st>>>(x, L, sc);
+    else row_absmax_kernel<1><<<ablocks, 256, 0, st>>>(x, L, sc);
+    if (int rc = check_launch()) return rc;
+    const dim3 grid((C + kGroup - 1) / kGroup, nrows);
+    const size_t smem = hist_smem_bytes(max_bins);
+#define CG_LAUNCH_Q(DT, V) \
+    quantize_cdf_kernel<DT, V><<<grid, kQuantThreads, smem, st>>>(x, L, bins, sc, max_bins, sym_out, cdf_out)
+    if (dtype == CG_F16) { if (vec) CG_LAUNCH_Q(CG_F16, 8); else CG_LAUNCH_Q(CG_F16, 1); }
+    else { if (vec) CG_LAUNCH_Q(CG_BF16, 8); else CG_LAUNCH_Q(CG_BF16, 1); }
+#undef CG_LAUNCH_Q
+    return check_launch();
+}

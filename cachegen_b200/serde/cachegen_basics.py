@@ -1,0 +1,154 @@
+"""CacheGenConfig and the wire dataclasses
+(reference: LMCache/lmcache/storage_backend/serde/cachegen_basics.py:8-156).
+
+The blob format is the reference's: `pickle` of a CacheGenGPUEncoderOutput whose tensors are CUDA
+tensors.  So that blobs travel both ways between this package and the reference, the two wire
+classes pickle under the reference's module path `lmcache.storage_backend.serde.cachegen_basics`;
+when no `lmcache` package is importable, alias modules of that name are registered at import time
+(see cachegen_b200.compat).
+"""
+import io
+import os
+import pickle
+from dataclasses import dataclass, replace
+from typing import List
+
+import torch
+
+CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK = 256
+
+REFERENCE_MODULE = "lmcache.storage_backend.serde.cachegen_basics"
+
+
+@dataclass
+class CacheGenConfig:
+    """Per-layer-group bin counts: keys in three groups, values in two (cachegen_basics.py:10-21)."""
+    key_first_layers: int
+    key_second_layers: int
+    key_third_layers: int
+    key_first_bins: int
+    key_second_bins: int
+    key_third_bins: int
+    value_first_layers: int
+    value_first_bins: int
+    value_second_bins: int
+
+    def __getitem__(self, key: str) -> int:
+        return getattr(self, key)
+
+    @property
+    def num_layers(self) -> int:
+        return self.key_third_layers
+
+    @property
+    def max_bins(self) -> int:
+        return max(self.key_first_bins, self.key_second_bins, self.key_third_bins,
+                   self.value_first_bins, self.value_second_bins)
+
+    def with_bins_divided(self, divisor: int, minimum: int = 4) -> "CacheGenConfig":
+        """A lower quality level: every bin count divided by `divisor`, not below `minimum`."""
+        d = lambda b: max(minimum, b // divisor)
+        return replace(self, key_first_bins=d(self.key_first_bins), key_second_bins=d(self.key_second_bins),
+                       key_third_bins=d(self.key_third_bins), value_first_bins=d(self.value_first_bins),
+                       value_second_bins=d(self.value_second_bins))
+
+    @staticmethod
+    def from_model_name(model_name: str) -> "CacheGenConfig":
+        """Same lookup as cachegen_basics.py:23-96: any name containing "Mistral-7B" reads the
+        QUANT_LEVEL environment variable ("1", "2" or "3"; KeyError when unset), the 7B and 70B
+        families have fixed settings, anything else raises ValueError."""
+        family_7b = ["mistralai/Mistral-7B-Instruct-v0.2", "mistral-community/Mistral-7B-v0.2",
+                     "lmsys/longchat-7b-16k"]
+        family_70b = ["Yukang/LongAlpaca-70B-16k"]
+        if "Mistral-7B" in model_name:
+            level = os.environ["QUANT_LEVEL"]
+            if level == "1":
+                return CacheGenConfig(10, 20, 32, 16, 16, 12, 2, 16, 12)
+            if level == "2":
+                return CacheGenConfig(10, 20, 32, 32, 16, 16, 2, 32, 16)
+            if level == "3":
+                return CacheGenConfig(10, 20, 32, 32, 32, 32, 2, 32, 32)
+            raise ValueError(f"QUANT_LEVEL must be 1, 2 or 3, got {level!r}")
+        elif model_name in family_7b:
+            return CacheGenConfig(10, 20, 32, 32, 16, 16, 2, 32, 16)
+        elif model_name in family_70b:
+            return CacheGenConfig(20, 40, 80, 32, 32, 16, 20, 32, 16)
+        else:
+            raise ValueError(f"Model {model_name} is not supported")
+
+
+def make_key_bins(config: CacheGenConfig, device="cuda") -> torch.Tensor:
+    """float32 [L] (cachegen_encoder.py:311-316 / cachegen_decoder.py:122-127)."""
+    ret = torch.zeros(config.key_third_layers)
+    ret.fill_(config.key_third_bins)
+    ret[:config.key_second_layers] = config.key_second_bins
+    ret[:config.key_first_layers] = config.key_first_bins
+    return ret.to(device)
+
+
+def make_value_bins(config: CacheGenConfig, device="cuda") -> torch.Tensor:
+    """float32 [L] (cachegen_encoder.py:318-322 / cachegen_decoder.py:129-135)."""
+    ret = torch.zeros(config.key_third_layers)
+    ret.fill_(config.value_second_bins)
+    ret[:config.value_first_layers] = config.value_first_bins
+    return ret.to(device)
+
+
+@dataclass
+class CacheGenGPUBytestream:
+    """One sub-chunk (<= 256 tokens) of encoded streams (cachegen_basics.py:124-131)."""
+    bytestream: torch.Tensor          # uint8 [sum of lengths]: streams in (row, channel) order
+    bytestream_lengths: torch.Tensor  # int32 [2L, C]
+    ntokens: int
+
+    def __getitem__(self, key: str):
+        return getattr(self, key)
+
+
+@dataclass
+class CacheGenGPUEncoderOutput:
+    """One encoded chunk (cachegen_basics.py:133-156)."""
+    data_chunks: List[CacheGenGPUBytestream]
+    cdf: torch.Tensor                # int16 [2L, C, Lp]
+    max_tensors_key: torch.Tensor    # [L, T, 1], input dtype
+    max_tensors_value: torch.Tensor  # [L, T, 1], input dtype
+    num_heads: int
+    head_size: int
+
+    def __getitem__(self, key: str):
+        return getattr(self, key)
+
+    def to_bytes(self) -> bytes:
+        with io.BytesIO() as f:
+            pickle.dump(self, f)
+            return f.getvalue()
+
+    @staticmethod
+    def from_bytes(bs: bytes) -> "CacheGenGPUEncoderOutput":
+        with io.BytesIO(bs) as f:
+            return _Unpickler(f).load()
+
+
+# `CacheGenEncoderOutput.from_bytes` is what the reference's tests call on a blob
+# (LMCache/tests/test_serde.py:43); with pickle it is the same loader.
+CacheGenEncoderOutput = CacheGenGPUEncoderOutput
+
+
+class _Unpickler(pickle.Unpickler):
+    """pickle loader that resolves the two wire classes to this module, whichever module path the
+    blob was written under."""
+
+    def find_class(self, module, name):
+        if name in ("CacheGenGPUEncoderOutput", "CacheGenGPUBytestream") and module in (REFERENCE_MODULE, __name__):
+            return globals()[name]
+        return super().find_class(module, name)
+
+
+def _adopt_reference_module_path():
+    from .. import compat
+    if compat.install_wire_aliases(__name__):
+        CacheGenGPUBytestream.__module__ = REFERENCE_MODULE
+        CacheGenGPUEncoderOutput.__module__ = REFERENCE_MODULE
+
+
+_adopt_reference_module_path()

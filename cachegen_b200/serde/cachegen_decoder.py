@@ -1,0 +1,253 @@
+"""CacheGenDeserializer (reference: LMCache/lmcache/storage_backend/serde/cachegen_decoder.py:114-173).
+
+`from_bytes` keeps the reference's contract -- pickled CacheGenGPUEncoderOutput in, KV blob tensor on
+the GPU out, bf16 [L,2,T,H,D] for "vllm" and fp16 [L,2,H,T,D] for "huggingface" -- with the
+per-sub-chunk launches and the fp32 dequantise / stack / permute / cast chain replaced by two C-ABI
+calls: cg_decode_offsets (the cumsum of dec.py:70) and cg_decode_dequant (everything else).
+(dec.py = cachegen_decoder.py of the reference.)
+"""
+import ctypes
+from typing import List
+
+import torch
+
+from .. import _lib
+from .. import torchac_cuda
+from ..config import LMCacheEngineConfig, LMCacheEngineMetadata
+from . import cachegen_basics as CGBasics
+from .cachegen_basics import CacheGenConfig, CacheGenGPUBytestream, CacheGenGPUEncoderOutput
+from .serde import Deserializer
+
+_DTYPES = {torch.float16: _lib.CG_F16, torch.bfloat16: _lib.CG_BF16}
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def do_dequantize(t: torch.Tensor, bins: torch.Tensor, maxtensors: torch.Tensor) -> torch.Tensor:
+    """The reference's dequantisation formula on torch tensors (dec.py:24-34); the product path
+    computes the same values inside cg_decode_dequant.  t [L,T,C] float, bins [L], maxtensors [L,T,1]."""
+    C = (bins // 2 - 1)[:, None, None]
+    t = t - C
+    t = t / C
+    t = t * maxtensors
+    return t
+
+
+def decode_chunk(cdf: torch.Tensor, data_chunk: CacheGenGPUBytestream, target_buffer: torch.Tensor) -> None:
+    """Symbols of one sub-chunk into target_buffer [2L, ntokens, C] uint8, strided ok (dec.py:53-75)."""
+    lengths = data_chunk.bytestream_lengths
+    length_prefsum = lengths.flatten().cumsum(0).reshape(lengths.shape)
+    torchac_cuda.decode_fast_prefsum(cdf, data_chunk.bytestream, length_prefsum, target_buffer)
+
+
+def decode_function_gpu(cdf: torch.Tensor, data_chunks: List[CacheGenGPUBytestream], layers_in_key: int,
+                        chunk_size: int, output: torch.Tensor):
+    """Symbol-level decode with the reference's signature (dec.py:78-112): fills `output`
+    (uint8 [chunk_size, 2L*C]) and returns (key, value) symbols as float32 [L, chunk_size, C]."""
+    nlayers, nchannels, _ = cdf.shape
+    output = output.reshape((nlayers, chunk_size, nchannels))
+    start = 0
+    for data_chunk in data_chunks:
+        end = start + data_chunk.ntokens
+        decode_chunk(cdf, data_chunk, output[:, start:end, :])
+        start = end
+    out = output.reshape((2, layers_in_key, chunk_size, nchannels))
+    key, value = out.float()
+    return key, value
+
+
+def _check_chunk(eo: CacheGenGPUEncoderOutput):
+    cdf = eo.cdf
+    if not cdf.is_cuda:
+        raise RuntimeError("CDF should be on GPU")
+    NL, C, lp = cdf.shape
+    L = NL // 2
+    mk, mv = eo.max_tensors_key, eo.max_tensors_value
+    T = mk.shape[1]
+    if eo.num_heads * eo.head_size != C or mk.shape[0] != L or mv.shape[0] != L or mv.shape[1] != T:
+        raise RuntimeError("inconsistent shapes in the encoded chunk")
+    if mk.dtype not in _DTYPES or mk.dtype != mv.dtype:
+        raise TypeError(f"scales must be float16 or bfloat16, got {mk.dtype} / {mv.dtype}")
+    if sum(dc.ntokens for dc in eo.data_chunks) != T:
+        raise RuntimeError("sub-chunk token counts do not add up to the chunk's tokens")
+    return L, C, lp, T
+
+
+def decode_many(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Tensor, fmt: str,
+                out_dtype: torch.dtype, out: torch.Tensor = None, workspace: dict = None) -> torch.Tensor:
+    """Fused decode of consecutive encoded chunks of one KV cache into one blob.
+
+    The chunks' tokens are laid one after the other along the token axis of the result, which has
+    shape [L,2,T,H,D] ("vllm") or [L,2,H,T,D] ("huggingface"), T the total token count -- what
+    LMCacheEngine.retrive builds with torch.cat from per-chunk from_bytes calls
+    (LMCache/lmcache/cache_engine.py:282-320 in the reference).  All sub-chunks of all chunks go
+    through cg_decode_offsets + cg_decode_dequant in batches of up to 48 per launch.
+
+    bins: float32 [2L] on the GPU (key bins then value bins).  `out`, when given, must have the result's
+    shape and dtype with a unit innermost stride (any other strides).  `workspace` caches the small
+    offset / status buffers between calls.
+    """
+    if not encoder_outputs:
+        raise RuntimeError("nothing to decode")
+    first = encoder_outputs[0]
+    L, C, lp, _ = _check_chunk(first)
+    NL = 2 * L
+    H, D = first.num_heads, first.head_size
+    dev = first.cdf.device
+    scale_dtype = first.max_tensors_key.dtype
+    total_T = 0
+    for eo in encoder_outputs:
+        l2, c2, lp2, T = _check_chunk(eo)
+        if (l2, c2, lp2, eo.num_heads, eo.max_tensors_key.dtype) != (L, C, lp, H, scale_dtype):
+            raise RuntimeError("chunks of one decode call must share layers, channels, table length and dtype")
+        total_T += T
+    if bins.numel() != NL:
+        raise RuntimeError(f"bins describe {bins.numel() // 2} layers, the blob has {L}")
+    shape = (L, 2, total_T, H, D) if fmt == "vllm" else (L, 2, H, total_T, D)
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=dev)
+    elif tuple(out.shape) != shape or out.dtype != out_dtype or out.stride(4) != 1 or out.device != dev:
+        raise RuntimeError("output tensor has the wrong shape, dtype, device or innermost stride")
+    if fmt == "vllm":
+        o_layer, o_kv, o_token, o_head = out.stride(0), out.stride(1), out.stride(2), out.stride(3)
+    else:
+        o_layer, o_kv, o_head, o_token = out.stride(0), out.stride(1), out.stride(2), out.stride(3)
+
+    nslab = (C + _lib.CG_GROUP_CHANNELS - 1) // _lib.CG_GROUP_CHANNELS
+    ngroups = NL * nslab
+    njobs_total = sum(len(eo.data_chunks) for eo in encoder_outputs)
+    ws = workspace if workspace is not None else {}
+    goff = ws.get("group_off")
+    if goff is None or goff.numel() < njobs_total * ngroups or goff.device != dev:
+        goff = torch.empty(njobs_total * ngroups, dtype=torch.int64, device=dev)
+        ws["group_off"] = goff
+    status = ws.get("status")
+    if status is None or status.device != dev:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        ws["status"] = status
+
+    esz = out.element_size()
+    keep = []  # tensors that must outlive the launches
+    jobs_all = []
+    t0 = 0
+    for eo in encoder_outputs:
+        T = eo.max_tensors_key.shape[1]
+        mk = eo.max_tensors_key.reshape(L, T).contiguous()
+        mv = eo.max_tensors_value.reshape(L, T).contiguous()
+        cdf = eo.cdf.contiguous()
+        keep += [mk, mv, cdf]
+        tc = 0
+        for dc in eo.data_chunks:
+            bs = dc.bytestream.contiguous()
+            ln = dc.bytestream_lengths.contiguous()
+            if ln.dtype != torch.int32 or ln.numel() != NL * C:
+                raise RuntimeError("bytestream_lengths must be int32 [2L, C]")
+            if bs.dtype != torch.uint8 or not bs.is_cuda or not ln.is_cuda:
+                raise RuntimeError("bytestream must be a uint8 CUDA tensor")
+            if not 0 < dc.ntokens <= CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK:
+                raise RuntimeError("a sub-chunk holds 1..256 tokens")
+            keep += [bs, ln]
+            job = _lib.DecodeJob()
+            job.cdf = cdf.data_ptr()
+            job.bytes = bs.data_ptr()
+            job.lengths = ln.data_ptr()
+            job.group_off = goff.data_ptr() + 8 * len(jobs_all) * ngroups
+            job.scales_k = mk.data_ptr() + mk.element_size() * tc
+            job.scales_v = mv.data_ptr() + mv.element_size() * tc
+            job.out = out.data_ptr() + esz * (t0 + tc) * o_token
+            job.nbytes = bs.numel()
+            job.ntokens = dc.ntokens
+            job.scale_stride = T
+            jobs_all.append(job)
+            tc += dc.ntokens
+        t0 += T
+    lib = _lib.lib()
+    with torch.cuda.device(dev):
+        st = _stream(dev)
+        for b in range(0, njobs_total, _lib.CG_MAX_DECODE_JOBS):
+            batch = jobs_all[b:b + _lib.CG_MAX_DECODE_JOBS]
+            arr = (_lib.DecodeJob * len(batch))(*batch)
+            rc = lib.cg_decode_offsets(arr, len(batch), NL, C, ctypes.c_void_p(goff.data_ptr() + 8 * b * ngroups),
+                                       ctypes.c_void_p(status.data_ptr()), st)
+            _lib.check(rc, "cg_decode_offsets")
+            rc = lib.cg_decode_dequant(arr, len(batch), L, H, D, lp, ctypes.c_void_p(bins.data_ptr()),
+                                       _DTYPES[scale_dtype], _DTYPES[out_dtype], o_layer, o_kv, o_token, o_head,
+                                       ctypes.c_void_p(status.data_ptr()), st)
+            _lib.check(rc, "cg_decode_dequant")
+    cur = torch.cuda.current_stream(dev)
+    for t in keep:
+        t.record_stream(cur)
+    return out
+
+
+def decode_to_kv(encoder_output: CacheGenGPUEncoderOutput, bins: torch.Tensor, fmt: str, out_dtype: torch.dtype,
+                 out: torch.Tensor = None, workspace: dict = None) -> torch.Tensor:
+    """Fused decode of one encoded chunk into its KV blob (see decode_many)."""
+    return decode_many([encoder_output], bins, fmt, out_dtype, out=out, workspace=workspace)
+
+
+class CacheGenDeserializer(Deserializer):
+    """Reference: dec.py:114-173.  `out_dtype` overrides the reference's fixed choice (bf16 for "vllm",
+    fp16 for "huggingface"); `cachegen_config` replaces the lookup by model name."""
+
+    def __init__(self, config: LMCacheEngineConfig, metadata: LMCacheEngineMetadata,
+                 cachegen_config: CacheGenConfig = None, out_dtype: torch.dtype = None):
+        _lib.lib()  # fail at construction if the CUDA library is missing
+        self.cachegen_config = cachegen_config or CacheGenConfig.from_model_name(metadata.model_name)
+        self.chunk_size = config.chunk_size
+        self.fmt = metadata.fmt
+        if self.fmt not in ("vllm", "huggingface"):
+            raise ValueError(f"unknown KV format {self.fmt!r}")
+        self.out_dtype = out_dtype or (torch.bfloat16 if self.fmt == "vllm" else torch.float16)
+        self.key_bins = self.make_key_bins(self.cachegen_config)
+        self.value_bins = self.make_value_bins(self.cachegen_config)
+        self._bins = torch.cat((self.key_bins, self.value_bins)).contiguous()
+        self._workspace = {}
+
+    def make_key_bins(self, config: CacheGenConfig) -> torch.Tensor:
+        return CGBasics.make_key_bins(config, "cuda")
+
+    def make_value_bins(self, config: CacheGenConfig) -> torch.Tensor:
+        return CGBasics.make_value_bins(config, "cuda")
+
+    def decode(self, encoder_output: CacheGenGPUEncoderOutput, out: torch.Tensor = None) -> torch.Tensor:
+        """`from_bytes` without the unpickling."""
+        ntokens = encoder_output.max_tensors_key.shape[1]
+        if ntokens > self.chunk_size:
+            # the reference slices a chunk_size-row buffer and fails in its reshape (dec.py:138-141,101)
+            raise RuntimeError(f"blob holds {ntokens} tokens, more than chunk_size = {self.chunk_size}")
+        dev = encoder_output.cdf.device
+        if self._bins.device != dev:
+            self._bins = self._bins.to(dev)
+        return decode_to_kv(encoder_output, self._bins, self.fmt, self.out_dtype, out=out, workspace=self._workspace)
+
+    def decode_many(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None) -> torch.Tensor:
+        """Consecutive chunks of one KV cache into one blob, in as few launches as possible."""
+        for eo in encoder_outputs:
+            if eo.max_tensors_key.shape[1] > self.chunk_size:
+                raise RuntimeError(f"a blob holds more tokens than chunk_size = {self.chunk_size}")
+        dev = encoder_outputs[0].cdf.device
+        if self._bins.device != dev:
+            self._bins = self._bins.to(dev)
+        return decode_many(encoder_outputs, self._bins, self.fmt, self.out_dtype, out=out, workspace=self._workspace)
+
+    def check_status(self) -> None:
+        """Synchronises and raises if a decode since the last check met malformed stream lengths."""
+        status = self._workspace.get("status")
+        if status is not None:
+            bits = int(status.item())
+            if bits:
+                status.zero_()
+                raise RuntimeError("cachegen decode: " + _lib.status_text(bits))
+
+    def from_bytes(self, bs: bytes) -> torch.Tensor:
+        encoder_output = CacheGenGPUEncoderOutput.from_bytes(bs)
+        encoder_output.cdf = encoder_output.cdf.cuda()
+        encoder_output.max_tensors_key = encoder_output.max_tensors_key.cuda()
+        encoder_output.max_tensors_value = encoder_output.max_tensors_value.cuda()
+        for dc in encoder_output.data_chunks:
+            dc.bytestream = dc.bytestream.cuda()
+            dc.bytestream_lengths = dc.bytestream_lengths.cuda()
+        return self.decode(encoder_output)

@@ -1,0 +1,168 @@
+"""CacheGenSerializer (reference: LMCache/lmcache/storage_backend/serde/cachegen_encoder.py:247-348).
+
+`to_bytes` keeps the reference's contract -- KV blob tensor in, pickled CacheGenGPUEncoderOutput out,
+byte-identical to what the reference produces from the same input -- with the reference's chain of
+torch ops and per-sub-chunk launches replaced by four C-ABI calls:
+
+    cg_quantize_cdf      split K/V + quantise + histogram + tables      (enc.py:257-267)
+    cg_encode_chunk      every sub-chunk's streams + offsets            (enc.py:269-292, 225-236)
+    cg_compact_streams   gather of the streams                          (enc.py:210-222)
+
+(enc.py = cachegen_encoder.py of the reference.)
+"""
+import ctypes
+from typing import Tuple
+
+import torch
+
+from .. import _lib
+from ..config import LMCacheEngineConfig, LMCacheEngineMetadata
+from . import cachegen_basics as CGBasics
+from .cachegen_basics import CacheGenConfig, CacheGenGPUBytestream, CacheGenGPUEncoderOutput
+from .serde import Serializer
+
+_DTYPES = {torch.float16: _lib.CG_F16, torch.bfloat16: _lib.CG_BF16}
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _split_kv(tensor: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """[L, 2, T, H, D] -> K and V as [L, T, H*D] (enc.py:72-83)."""
+    num_layers, _, num_tokens, num_heads, head_size = tensor.shape
+    return torch.unbind(tensor.reshape(num_layers, 2, num_tokens, num_heads * head_size), dim=1)
+
+
+def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor, max_bins: int):
+    """Fused torch_quant_vectorized (K and V) + calculate_cdf (K and V) + the two torch.cat of
+    encode_function (enc.py:42-59, 257-267).
+
+    kv: CUDA fp16/bf16 blob addressed as [L, 2, T, H, D] (any strides with a unit innermost stride, so
+        the permuted view of a "huggingface" blob is read in place).
+    Returns (symbols int8 [2L, T, C], scales [2L, T] in kv.dtype, tables int16 [2L, C, max_bins + 1]).
+    """
+    if kv.dim() != 5 or kv.shape[1] != 2:
+        raise RuntimeError(f"expected a KV blob of shape [L, 2, T, H, D], got {tuple(kv.shape)}")
+    if kv.dtype not in _DTYPES:
+        raise TypeError(f"the codec takes float16 or bfloat16 KV, got {kv.dtype}")
+    if not kv.is_cuda:
+        raise RuntimeError("KV must be a CUDA tensor")
+    if kv.stride(4) != 1:
+        kv = kv.contiguous()
+    L, _, T, H, D = kv.shape
+    C = H * D
+    dev = kv.device
+    bins = torch.cat((key_bins, value_bins)).to(device=dev, dtype=torch.float32).contiguous()
+    if bins.numel() != 2 * L:
+        raise RuntimeError(f"bins describe {bins.numel() // 2} layers, the KV blob has {L}")
+    sym = torch.empty((2 * L, T, C), dtype=torch.int8, device=dev)
+    scales = torch.empty((2 * L, T), dtype=kv.dtype, device=dev)
+    cdf = torch.empty((2 * L, C, max_bins + 1), dtype=torch.int16, device=dev)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().cg_quantize_cdf(_ptr(kv), _DTYPES[kv.dtype], kv.stride(0), kv.stride(1), kv.stride(2),
+                                        kv.stride(3), L, T, H, D, _ptr(bins), int(max_bins), _ptr(sym),
+                                        _ptr(scales), _ptr(cdf), _stream(dev))
+    _lib.check(rc, "cg_quantize_cdf")
+    return sym, scales, cdf
+
+
+def encode_streams(cdf: torch.Tensor, sym: torch.Tensor, scratch_stride: int = None):
+    """The sub-chunk loop of encode_function in one pass (enc.py:269-292).
+
+    cdf int16 [2L, C, Lp], sym int8 [2L, T, C] contiguous.  Returns (bytes uint8 [total], lengths int32
+    [nsub, 2L, C], sub_off: python list of nsub+1 byte offsets of the sub-chunks inside `bytes`).
+    Synchronises once, to size the output.
+    """
+    NL, T, C = sym.shape
+    lp = cdf.shape[2]
+    dev = sym.device
+    nsub = (T + CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK - 1) // CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK
+    stride = scratch_stride or _lib.stream_capacity(min(T, CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK))
+    stride = (stride + 3) // 4 * 4
+    nslab = (C + _lib.CG_GROUP_CHANNELS - 1) // _lib.CG_GROUP_CHANNELS
+    scratch = torch.empty((nsub, NL * C, stride), dtype=torch.uint8, device=dev)
+    lengths = torch.empty((nsub, NL, C), dtype=torch.int32, device=dev)
+    group_off = torch.empty((nsub, NL * nslab), dtype=torch.int64, device=dev)
+    sub_off = torch.empty(nsub + 1, dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        rc = L.cg_encode_chunk(_ptr(cdf), _ptr(sym), NL, T, C, lp, _ptr(scratch), stride, _ptr(lengths),
+                               _ptr(group_off), _ptr(sub_off), _ptr(status), _stream(dev))
+        _lib.check(rc, "cg_encode_chunk")
+        host = torch.cat((sub_off, status.to(torch.int64))).cpu()  # the one synchronisation
+        bits = int(host[-1])
+        if bits:
+            raise RuntimeError("cachegen encode: " + _lib.status_text(bits))
+        offs = [int(v) for v in host[:-1]]
+        out = torch.empty(offs[-1], dtype=torch.uint8, device=dev)
+        rc = L.cg_compact_streams(_ptr(scratch), stride, _ptr(lengths), _ptr(group_off), _ptr(sub_off), nsub, NL,
+                                  C, _ptr(out), _stream(dev))
+        _lib.check(rc, "cg_compact_streams")
+    return out, lengths, offs
+
+
+def encode_function(kv: torch.Tensor, config: CacheGenConfig, key_bins: torch.Tensor, value_bins: torch.Tensor,
+                    chunk_size: int) -> CacheGenGPUEncoderOutput:
+    """Encodes one chunk of KV, [L, 2, T, H, D] on the GPU, T == chunk_size (enc.py:247-301)."""
+    num_heads, head_size = kv.shape[-2:]
+    L = kv.shape[0]
+    if kv.shape[2] != chunk_size:
+        raise RuntimeError(f"chunk_size {chunk_size} does not match the {kv.shape[2]} tokens of the blob")
+    # the reference builds K and V tables with their own max and concatenates them, which needs the
+    # two to be equal (enc.py:265-267)
+    kmax, vmax = int(key_bins.max()), int(value_bins.max())
+    if kmax != vmax:
+        raise RuntimeError(f"Sizes of tensors must match: key tables have {kmax + 1} entries, value tables {vmax + 1}")
+    sym, scales, cdf = quantize_and_tables(kv, key_bins, value_bins, kmax)
+    stream_bytes, lengths, offs = encode_streams(cdf, sym)
+    data_chunks = []
+    step = CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK
+    nsub = len(offs) - 1
+    for j in range(nsub):
+        piece = stream_bytes[offs[j]:offs[j + 1]]
+        data_chunks.append(CacheGenGPUBytestream(
+            bytestream=piece if nsub == 1 else piece.clone(),  # a view would pickle the whole buffer
+            bytestream_lengths=lengths[j] if nsub == 1 else lengths[j].clone(),
+            ntokens=min(step, chunk_size - j * step)))
+    return CacheGenGPUEncoderOutput(
+        data_chunks, cdf,
+        max_tensors_key=scales[:L].clone().unsqueeze(-1),
+        max_tensors_value=scales[L:].clone().unsqueeze(-1),
+        num_heads=num_heads, head_size=head_size)
+
+
+class CacheGenSerializer(Serializer):
+    """Reference: enc.py:303-348.  `cachegen_config` may be given instead of looking it up from
+    metadata.model_name (quality levels other than the built-in ones)."""
+
+    def __init__(self, config: LMCacheEngineConfig, metadata: LMCacheEngineMetadata,
+                 cachegen_config: CacheGenConfig = None):
+        _lib.lib()  # fail at construction if the CUDA library is missing
+        self.cachegen_config = cachegen_config or CacheGenConfig.from_model_name(metadata.model_name)
+        self.chunk_size = config.chunk_size
+        self.fmt = metadata.fmt
+        self.key_bins = self.make_key_bins(self.cachegen_config)
+        self.value_bins = self.make_value_bins(self.cachegen_config)
+
+    def make_key_bins(self, config: CacheGenConfig) -> torch.Tensor:
+        return CGBasics.make_key_bins(config, "cuda")
+
+    def make_value_bins(self, config: CacheGenConfig) -> torch.Tensor:
+        return CGBasics.make_value_bins(config, "cuda")
+
+    def encode(self, tensor: torch.Tensor) -> CacheGenGPUEncoderOutput:
+        """`to_bytes` without the final pickle: the encoded chunk with its tensors on the GPU."""
+        if self.fmt == "huggingface":
+            tensor = tensor.permute(0, 1, 3, 2, 4)  # a view; the kernels read it through its strides
+        ntokens = tensor.shape[2]
+        return encode_function(tensor.cuda(), self.cachegen_config, self.key_bins, self.value_bins, ntokens)
+
+    def to_bytes(self, tensor: torch.Tensor) -> bytes:
+        """KV blob ([L,2,T,H,D] for "vllm", [L,2,H,T,D] for "huggingface") -> pickled bytes (enc.py:324-348)."""
+        return self.encode(tensor).to_bytes()

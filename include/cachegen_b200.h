@@ -1,0 +1,224 @@
+/*
+ * cachegen_b200 -- C ABI of the B200-native CacheGen KV-cache codec.
+ *
+ * One shared library (libcachegen_b200.so, sm_100a) exports exactly the calls a
+ * binding for the reference's codec path needs: the four `torchac_cuda` entry
+ * points (LMCache/third_party/torchac_cuda/main.cpp:14-17 in the reference) and
+ * the fused calls that replace the chains of torch ops around them in
+ * LMCache/lmcache/storage_backend/serde/cachegen_{encoder,decoder}.py.
+ *
+ * Conventions
+ *  - plain pointers and sizes only; every pointer is a DEVICE pointer unless its
+ *    name ends in `_host`; `stream` is a cudaStream_t passed as void* (NULL =
+ *    the legacy default stream);
+ *  - a call only enqueues work on `stream` and returns; results are valid after
+ *    the stream is synchronised; nothing is allocated, the caller owns all memory;
+ *  - return value: 0 = enqueued, < 0 = rejected argument (CG_E_*), nothing was
+ *    launched.  Conditions only the GPU can see (a stream that outgrew its
+ *    scratch row, lengths that do not add up) are OR-ed into the caller's
+ *    `status` word (int32 in device memory, may be NULL) as CG_S_* bits;
+ *  - strides are in ELEMENTS of the array they describe;
+ *  - 16-bit float type codes: CG_F16 = 0, CG_BF16 = 1;
+ *  - a "row" is one of the NL = 2*L rows of the codec's working tensors: the L
+ *    key layers followed by the L value layers (torch.cat((new_key, new_value)),
+ *    cachegen_encoder.py:263);
+ *  - a "stream" is the arithmetic-coded bitstream of one (row, channel) over the
+ *    <= CG_MAX_TOKENS_PER_STREAM tokens of one sub-chunk.
+ */
+#ifndef CACHEGEN_B200_H
+#define CACHEGEN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CG_F16 0
+#define CG_BF16 1
+
+/* cachegen_basics.py:8 CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK; torchac_kernel_enc_new.cu:10 */
+#define CG_MAX_TOKENS_PER_STREAM 256
+/* torchac_kernel_dec_new.cu:6 MAX_LP (the encoder's limit is 48, torchac_kernel_enc_new.cu:6) */
+#define CG_MAX_LP 64
+/* worst-case stream length for n tokens: 16 bits per symbol plus the flush */
+#define CG_STREAM_CAPACITY(ntokens) (2 * (ntokens) + 8)
+/* channels of one row handled by one thread block (one thread per stream) */
+#define CG_GROUP_CHANNELS 128
+/* sub-chunks one fused decode launch can take */
+#define CG_MAX_DECODE_JOBS 48
+
+/* argument errors (returned) */
+#define CG_OK 0
+#define CG_E_NULL (-1)        /* a required pointer is NULL */
+#define CG_E_SHAPE (-2)       /* non-positive or inconsistent extent */
+#define CG_E_TOKENS (-3)      /* more than CG_MAX_TOKENS_PER_STREAM tokens in a coder call */
+#define CG_E_LP (-4)          /* CDF length outside [2, CG_MAX_LP] / max_bins outside [1, 63] */
+#define CG_E_ALIGN (-5)       /* pointer or stride breaks an alignment rule of the call */
+#define CG_E_CAPACITY (-6)    /* scratch / workspace too small, or too many jobs */
+#define CG_E_DTYPE (-7)       /* unknown 16-bit float code */
+#define CG_E_CUDA (-8)        /* the CUDA runtime refused the launch; see cg_last_cuda_error */
+#define CG_E_HIST (-9)        /* ntokens >= 65536: the reference's uint16 histogram would wrap */
+
+/* device-reported conditions (bits OR-ed into *status) */
+#define CG_S_STREAM_OVERFLOW 1 /* an encoded stream needed more bytes than its scratch row */
+#define CG_S_BAD_LENGTHS 2     /* negative length, or lengths reach past the byte array */
+#define CG_S_BAD_SYMBOL 4      /* a symbol outside [0, Lp-2] was met while encoding */
+
+const char *cg_version(void);
+const char *cg_status_string(int code);
+/* text of the last CUDA runtime error seen by this library on the calling thread */
+const char *cg_last_cuda_error(void);
+
+/* ------------------------------------------------------------------------------------------
+ * torchac_cuda entry points
+ * ------------------------------------------------------------------------------------------ */
+
+/*
+ * Replaces torchac_cuda.calculate_cdf (cal_cdf.cu:68-129, kernel cal_cdf.cu:17-59).
+ * sym: int8 [nrows, ntokens, nchannels] with element strides sym_strides[3];
+ * cdf_out: int16 [nrows, nchannels, max_bins + 1], contiguous.
+ * cdf[i] = (uint16)((0xFFFF - max_bins) * #{sym < i} / ntokens) + i.  max_bins < 64 as in
+ * cal_cdf.cu:73; ntokens < 65536 (the reference's uint16 counters wrap there).
+ */
+int cg_calculate_cdf(const int8_t *sym, const int64_t sym_strides[3], int nrows, int ntokens,
+                     int nchannels, int max_bins, int16_t *cdf_out, void *stream);
+
+/*
+ * Replaces torchac_cuda.encode_fast_new (torchac_kernel_enc_new.cu:355-451, kernel :222-325).
+ * cdf: int16 [nrows, nchannels, lp]; sym: int8 [nrows, ntokens, nchannels] (strided);
+ * out_buf: uint8 [nrows, nchannels, out_stride], out_stride a multiple of 4 and out_buf 4-byte
+ * aligned; out_lengths: int32 [nrows, nchannels].  Bytes of a row past the stream's length are
+ * left as they were (the reference zero-fills nothing either).  A stream that needs more than
+ * out_stride bytes is truncated, its full length is still reported and CG_S_STREAM_OVERFLOW is
+ * raised (the reference overruns its 256-byte shared-memory row silently).
+ */
+int cg_encode_padded(const int16_t *cdf, const int8_t *sym, const int64_t sym_strides[3],
+                     int nrows, int ntokens, int nchannels, int lp, uint8_t *out_buf,
+                     int64_t out_stride, int32_t *out_lengths, int32_t *status, void *stream);
+
+/*
+ * Replaces torchac_cuda.decode_fast_new (torchac_kernel_dec_new.cu:314-393, kernel :75-186).
+ * streams: uint8 [nrows, nchannels, stream_stride]; lengths: int32 [nrows, nchannels];
+ * out: uint8 symbols [nrows, ntokens, nchannels] with element strides out_strides[3].
+ * Reads past a stream's length see zero bits (torchac_kernel_dec_new.cu:229-232).
+ */
+int cg_decode_padded(const int16_t *cdf, const uint8_t *streams, int64_t stream_stride,
+                     const int32_t *lengths, uint8_t *out, const int64_t out_strides[3],
+                     int nrows, int ntokens, int nchannels, int lp, int32_t *status, void *stream);
+
+/*
+ * Replaces torchac_cuda.decode_fast_prefsum (torchac_kernel_dec_new.cu:403-479, kernel :189-304).
+ * bytes: uint8 [nbytes], the streams back to back in (row, channel) order;
+ * prefsum: int64 [nrows, nchannels], INCLUSIVE prefix sum of the stream lengths
+ * (cachegen_decoder.py:70); stream g spans [prefsum[g-1], prefsum[g]), from 0 for g = 0.
+ */
+int cg_decode_prefsum(const int16_t *cdf, const uint8_t *bytes, int64_t nbytes,
+                      const int64_t *prefsum, uint8_t *out, const int64_t out_strides[3],
+                      int nrows, int ntokens, int nchannels, int lp, int32_t *status,
+                      void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * fused encode side
+ * ------------------------------------------------------------------------------------------ */
+
+/*
+ * Replaces _split_kv + torch_quant_vectorized (x2) + torch.cat + calculate_cdf (x2) + torch.cat
+ * of encode_function (cachegen_encoder.py:72-83,42-59,257-267) in two launches.
+ *
+ * kv: 16-bit floats, element (layer l, k/v j, token t, head h, d) at
+ *     kv[l*s_layer + j*s_kv + t*s_token + h*s_head + d]  (innermost stride 1).
+ *     "vllm" blob [L,2,T,H,D]: s_layer=2*T*H*D, s_kv=T*H*D, s_token=H*D, s_head=D.
+ *     "huggingface" blob [L,2,H,T,D]: s_layer=2*H*T*D, s_kv=H*T*D, s_token=D, s_head=T*D.
+ * bins: float32 [2*L] on the device, key bins then value bins (make_key_bins / make_value_bins,
+ *     cachegen_encoder.py:311-322).
+ * sym_out: int8 [2L, T, C] contiguous, C = H*D;  scales_out: 16-bit [2L, T] (max_tensors_key
+ *     then max_tensors_value, same dtype as kv);  cdf_out: int16 [2L, C, max_bins+1].
+ * The reference builds key and value tables with their own max_bins and concatenates them,
+ * which only works when both are equal (cachegen_encoder.py:265-267); pass that one value.
+ */
+int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
+                    int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
+                    const float *bins, int max_bins, int8_t *sym_out, void *scales_out,
+                    int16_t *cdf_out, void *stream);
+
+/*
+ * Replaces the sub-chunk loop of encode_function: encode_fast_new + the length bookkeeping of
+ * collect_bytes for every sub-chunk of a chunk (cachegen_encoder.py:269-292,210-242).
+ * sym: int8 [nrows, ntokens, nchannels] contiguous, ntokens any positive number; the chunk is cut
+ * in nsub = ceil(ntokens / 256) sub-chunks, all coded with the one table set `cdf`.
+ * scratch: uint8 [nsub, nrows*nchannels, scratch_stride]  (scratch_stride % 4 == 0;
+ *     CG_STREAM_CAPACITY(256) can never overflow);
+ * lengths_out: int32 [nsub, nrows, nchannels];
+ * group_off_out: int64 [nsub, ngroups], ngroups = nrows * ceil(nchannels / 128): exclusive byte
+ *     offset, within its own sub-chunk, of the first stream of every 128-channel group;
+ * sub_off_out: int64 [nsub + 1]: byte offset of every sub-chunk in the concatenation of all
+ *     sub-chunks; the last entry is the total payload size.
+ */
+int cg_encode_chunk(const int16_t *cdf, const int8_t *sym, int nrows, int ntokens, int nchannels,
+                    int lp, uint8_t *scratch, int64_t scratch_stride, int32_t *lengths_out,
+                    int64_t *group_off_out, int64_t *sub_off_out, int32_t *status, void *stream);
+
+/*
+ * Second half of collect_bytes (cachegen_encoder.py:210-222): gathers the first `length` bytes of
+ * every scratch row into bytes_out (uint8, sub_off[nsub] bytes, as sized by the caller after
+ * reading sub_off_out of cg_encode_chunk), streams back to back in (sub-chunk, row, channel) order.
+ * lengths, group_off and sub_off are the arrays cg_encode_chunk wrote.
+ */
+int cg_compact_streams(const uint8_t *scratch, int64_t scratch_stride, const int32_t *lengths,
+                       const int64_t *group_off, const int64_t *sub_off, int nsub, int nrows,
+                       int nchannels, uint8_t *bytes_out, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * fused decode side
+ * ------------------------------------------------------------------------------------------ */
+
+/* One sub-chunk (CacheGenGPUBytestream, cachegen_basics.py:124-131) of one encoded chunk. */
+typedef struct cg_decode_job {
+    const int16_t *cdf;      /* [nrows, nchannels, lp] table set of the chunk */
+    const uint8_t *bytes;    /* the sub-chunk's streams, back to back */
+    const int32_t *lengths;  /* [nrows, nchannels] stream lengths (bytestream_lengths) */
+    const int64_t *group_off;/* [nrows*ceil(nchannels/128)] exclusive byte offset of each
+                                128-channel group inside `bytes`: written by cg_decode_offsets */
+    const void *scales_k;    /* 16-bit [nlayers, scale_stride]: max_tensors_key, at this
+                                sub-chunk's first token */
+    const void *scales_v;    /* 16-bit [nlayers, scale_stride]: max_tensors_value, likewise */
+    void *out;               /* 16-bit KV, element (layer 0, key, this sub-chunk's first token,
+                                head 0, d 0) of the output blob */
+    int64_t nbytes;          /* size of `bytes` */
+    int32_t ntokens;         /* tokens in this sub-chunk, 1..256 */
+    int32_t scale_stride;    /* elements between consecutive layers in scales_k / scales_v */
+} cg_decode_job;
+
+/*
+ * Exclusive offsets of every 128-channel group of every job (the cumsum of
+ * cachegen_decoder.py:70, computed per group instead of per stream).  Writes
+ * group_off_out[j * ngroups + g] for the njobs jobs; fill cg_decode_job.group_off with
+ * group_off_out + j * ngroups.  Only jobs[].lengths and jobs[].nbytes are read.
+ * Raises CG_S_BAD_LENGTHS when a job's lengths are negative or do not sum to its nbytes.
+ */
+int cg_decode_offsets(const cg_decode_job *jobs_host, int njobs, int nrows, int nchannels,
+                      int64_t *group_off_out, int32_t *status, void *stream);
+
+/*
+ * Replaces decode_function_gpu + do_dequantize (x2) + torch.stack + reshape + permute + cast of
+ * CacheGenDeserializer.from_bytes (cachegen_decoder.py:78-112,24-34,159-173) in one launch:
+ * arithmetic decode, (sym - Cq) / Cq * max in fp32, one round-to-nearest cast, store into the
+ * final KV blob.
+ * Output element (layer l, k/v j, token t, head h, d) of a job is written at
+ *     job.out[l*o_layer + j*o_kv + t*o_token + h*o_head + d]
+ * (strides as for cg_quantize_cdf; "vllm" gives [L,2,T,H,D], "huggingface" [L,2,H,T,D]).
+ * bins: float32 [2*nlayers] on the device (key bins then value bins, cachegen_decoder.py:122-135);
+ * scale_dtype: type of scales_k / scales_v; out_dtype: type of the output
+ * (the reference returns bf16 for "vllm" and fp16 for "huggingface", cachegen_decoder.py:169-173).
+ * njobs <= CG_MAX_DECODE_JOBS; all jobs share nlayers, nheads, head_size, lp and the strides.
+ */
+int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int nlayers, int nheads,
+                      int head_size, int lp, const float *bins, int scale_dtype, int out_dtype,
+                      int64_t o_layer, int64_t o_kv, int64_t o_token, int64_t o_head,
+                      int32_t *status, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CACHEGEN_B200_H */

@@ -1,0 +1,111 @@
+"""The C-ABI library loads without a GPU and exports every function include/cachegen_b200.h declares;
+argument errors are rejected before anything touches CUDA."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from cachegen_b200 import build, _lib
+    build.build()
+    return _lib.lib()
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "cachegen_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(cg_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree(lib):
+    from cachegen_b200 import _lib
+    names = declared_functions()
+    assert len(names) >= 12
+    assert sorted(_lib.EXPORTS) == names
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_version_and_status_strings(lib):
+    assert b"sm_100a" in lib.cg_version()
+    assert lib.cg_status_string(0) == b"ok"
+    for code in range(-9, 0):
+        assert lib.cg_status_string(code) != b"unknown status"
+
+
+def test_argument_errors_need_no_gpu(lib):
+    from cachegen_b200 import _lib
+    s3 = (ctypes.c_int64 * 3)(1, 1, 1)
+    one = ctypes.c_void_p(16)  # never dereferenced: every call below is rejected before launching
+    assert lib.cg_calculate_cdf(None, s3, 1, 1, 1, 4, one, None) == -1
+    assert lib.cg_calculate_cdf(one, s3, 1, 1, 1, 64, one, None) == -4
+    assert lib.cg_calculate_cdf(one, s3, 1, 65536, 1, 4, one, None) == -9
+    assert lib.cg_calculate_cdf(one, s3, 0, 1, 1, 4, one, None) == -2
+    assert lib.cg_encode_padded(one, one, s3, 1, 257, 1, 33, one, 256, one, None, None) == -3
+    assert lib.cg_encode_padded(one, one, s3, 1, 256, 1, 65, one, 256, one, None, None) == -4
+    assert lib.cg_encode_padded(one, one, s3, 1, 256, 1, 33, one, 255, one, None, None) == -5
+    assert lib.cg_decode_prefsum(one, one, 8, None, one, s3, 1, 1, 1, 33, None, None) == -1
+    assert lib.cg_decode_prefsum(one, one, 8, one, one, s3, 1, 300, 1, 33, None, None) == -3
+    assert lib.cg_decode_padded(one, one, 0, one, one, s3, 1, 1, 1, 33, None, None) == -2
+    assert lib.cg_quantize_cdf(one, 7, 1, 1, 1, 1, 1, 1, 1, 1, one, 32, one, one, one, None) == -7
+    assert lib.cg_quantize_cdf(one, 0, 1, 1, 1, 1, 1, 70000, 1, 1, one, 32, one, one, one, None) == -9
+    assert lib.cg_encode_chunk(one, one, 1, 1, 1, 33, one, 10, one, one, one, None, None) == -5
+    assert lib.cg_compact_streams(one, 8, one, one, one, 0, 1, 1, one, None) == -2
+    jobs = (_lib.DecodeJob * 1)()
+    assert lib.cg_decode_offsets(jobs, 49, 1, 1, one, None, None) == -6
+    assert lib.cg_decode_offsets(jobs, 1, 1, 1, one, None, None) == -1   # job.lengths is NULL
+    assert lib.cg_decode_dequant(jobs, 1, 1, 1, 1, 33, one, 0, 5, 1, 1, 1, 1, None, None) == -7
+    assert lib.cg_decode_dequant(jobs, 1, 1, 1, 1, 33, one, 0, 0, 1, 1, 1, 1, None, None) == -1
+
+
+def test_product_has_no_oracle_dependency():
+    """Nothing under cachegen_b200/ may import or load the oracle."""
+    for dirpath, _, files in os.walk(os.path.join(ROOT, "cachegen_b200")):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "cg_oracle" not in text and "libcg_oracle" not in text, f
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", text, flags=re.M), f
+
+
+def test_config_lookup(monkeypatch, golden_cpu):
+    import torch
+    from cachegen_b200.serde.cachegen_basics import CacheGenConfig, make_key_bins, make_value_bins
+    monkeypatch.setenv("QUANT_LEVEL", "2")
+    for name in ("lmsys/longchat-7b-16k", "Yukang/LongAlpaca-70B-16k", "mistralai/Mistral-7B-Instruct-v0.2"):
+        cfg = CacheGenConfig.from_model_name(name)
+        key = name.split("/")[1]
+        assert (make_key_bins(cfg, "cpu").numpy() == golden_cpu[f"bins_{key}_k"]).all()
+        assert (make_value_bins(cfg, "cpu").numpy() == golden_cpu[f"bins_{key}_v"]).all()
+    monkeypatch.setenv("QUANT_LEVEL", "1")
+    assert CacheGenConfig.from_model_name("x/Mistral-7B-y").key_third_bins == 12
+    monkeypatch.delenv("QUANT_LEVEL")
+    with pytest.raises(KeyError):
+        CacheGenConfig.from_model_name("mistralai/Mistral-7B-Instruct-v0.2")
+    with pytest.raises(ValueError):
+        CacheGenConfig.from_model_name("gpt2")
+    half = CacheGenConfig.from_model_name("lmsys/longchat-7b-16k").with_bins_divided(2)
+    assert (half.key_first_bins, half.key_second_bins, half.value_second_bins) == (16, 8, 8)
+    quarter = CacheGenConfig.from_model_name("lmsys/longchat-7b-16k").with_bins_divided(4)
+    assert (quarter.key_first_bins, quarter.key_third_bins) == (8, 4)
+    assert isinstance(make_key_bins(half, "cpu"), torch.Tensor)
+
+
+def test_wire_classes_pickle_under_the_reference_path():
+    import torch
+    from cachegen_b200.serde.cachegen_basics import CacheGenGPUBytestream, CacheGenGPUEncoderOutput, CacheGenEncoderOutput
+    o = CacheGenGPUEncoderOutput([CacheGenGPUBytestream(torch.zeros(3, dtype=torch.uint8),
+                                                        torch.ones(2, 2, dtype=torch.int32), 5)],
+                                 torch.zeros(2, 2, 3, dtype=torch.int16), torch.zeros(1, 5, 1), torch.ones(1, 5, 1), 1, 2)
+    blob = o.to_bytes()
+    import sys
+    if getattr(sys.modules.get("lmcache"), "__cachegen_b200_alias__", False):  # no real lmcache installed
+        assert b"lmcache.storage_backend.serde.cachegen_basics" in blob
+    back = CacheGenEncoderOutput.from_bytes(blob)
+    assert back.num_heads == 1 and back.head_size == 2 and back.data_chunks[0].ntokens == 5
+    assert back["cdf"].shape == (2, 2, 3) and back.data_chunks[0]["bytestream_lengths"].sum() == 4

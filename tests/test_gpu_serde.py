@@ -1,0 +1,186 @@
+"""The fused product path (cg_quantize_cdf / cg_encode_chunk / cg_compact_streams / cg_decode_offsets /
+cg_decode_dequant) and the serializer classes on the GPU against the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import bits_np, kv_rows
+
+pytestmark = pytest.mark.gpu
+
+MODEL_7B = "lmsys/longchat-7b-16k"
+
+
+def make_serde(chunk_size, fmt, model=MODEL_7B, **kw):
+    from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
+    from cachegen_b200.serde import CacheGenDeserializer, CacheGenSerializer
+    config = LMCacheEngineConfig.from_defaults(chunk_size=chunk_size)
+    metadata = LMCacheEngineMetadata(model_name=model, world_size=1, worker_id=0, fmt=fmt)
+    ser_kw = {k: v for k, v in kw.items() if k == "cachegen_config"}
+    return CacheGenSerializer(config, metadata, **ser_kw), CacheGenDeserializer(config, metadata, **kw)
+
+
+def oracle_encode(oracle, kv_cpu, key_bins, value_bins, dtype_code):
+    """The reference pipeline on the CPU oracle for a vllm-format blob -> dict of numpy results."""
+    rows = kv_rows(kv_cpu)
+    bins = np.concatenate((key_bins, value_bins)).astype(np.float32)
+    sym, mx = oracle.quantize(bits_np(rows), bins, dtype_code)
+    cdf = oracle.calculate_cdf(sym, int(bins.max()))
+    chunks = []
+    T = rows.shape[1]
+    for s in range(0, T, 256):
+        e = min(s + 256, T)
+        chunks.append(oracle.encode_chunk(cdf, sym[:, s:e, :]))
+    return dict(sym=sym, max=mx, cdf=cdf, chunks=chunks, bins=bins)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("T", [1, 16, 236, 256, 700])
+def test_encode_is_bit_exact_and_decode_matches_reference_formula(oracle, dtype, T):
+    from cachegen_b200.synth import generate_kv
+    code = oracle.F16 if dtype == torch.float16 else oracle.BF16
+    L, H, D = 32, 2, 64
+    kv = generate_kv(L, H, D, T, seed=T, device="cpu", dtype=dtype)
+    kv[3, 0, T // 2] = 0  # an all-zero token row
+    ser, de = make_serde(max(T, 256), "vllm")
+    eo = ser.encode(kv.cuda())
+    ref = oracle_encode(oracle, kv, ser.key_bins.cpu().numpy(), ser.value_bins.cpu().numpy(), code)
+
+    assert (eo.cdf.cpu().numpy() == ref["cdf"]).all()
+    assert (bits_np(eo.max_tensors_key).reshape(L, T) == ref["max"][:L].reshape(L, T)).all()
+    assert (bits_np(eo.max_tensors_value).reshape(L, T) == ref["max"][L:].reshape(L, T)).all()
+    assert eo.max_tensors_key.dtype == dtype and tuple(eo.max_tensors_key.shape) == (L, T, 1)
+    assert len(eo.data_chunks) == len(ref["chunks"])
+    for dc, (want_bytes, want_len) in zip(eo.data_chunks, ref["chunks"]):
+        assert (dc.bytestream_lengths.cpu().numpy() == want_len).all()
+        assert dc.bytestream.cpu().numpy().tobytes() == want_bytes.tobytes()
+        assert dc.bytestream.dtype == torch.uint8 and dc.bytestream_lengths.dtype == torch.int32
+
+    # decode: exact equality with the reference's fp32 formula + one cast, in every output type
+    for out_dtype, out_code in ((torch.float16, oracle.F16), (torch.bfloat16, oracle.BF16)):
+        de.out_dtype = out_dtype
+        got = de.decode(eo)
+        de.check_status()
+        assert got.dtype == out_dtype and tuple(got.shape) == tuple(kv.shape)
+        want = oracle.dequantize(ref["sym"].view(np.uint8), ref["bins"], ref["max"], code, out_code)
+        assert (bits_np(kv_rows(got)) == want).all()
+
+
+@pytest.mark.parametrize("fmt", ["vllm", "huggingface"])
+def test_formats_agree_and_blobs_round_trip_through_pickle(oracle, fmt):
+    from cachegen_b200.serde.cachegen_basics import CacheGenEncoderOutput
+    from cachegen_b200.synth import generate_kv
+    L, H, D, T = 32, 8, 128, 128
+    kv = generate_kv(L, H, D, T, seed=5, device="cpu", dtype=torch.float16).cuda()
+    ser_v, de_v = make_serde(256, "vllm", out_dtype=torch.float16)
+    ser_h, de_h = make_serde(256, "huggingface")
+    blob_v = ser_v.to_bytes(kv)
+    kv_h = kv.permute(0, 1, 3, 2, 4).contiguous()
+    blob_h = ser_h.to_bytes(kv_h)
+    assert len(blob_v) == len(blob_h)
+    a, b = CacheGenEncoderOutput.from_bytes(blob_v), CacheGenEncoderOutput.from_bytes(blob_h)
+    assert a.num_heads == H and a.head_size == D
+    assert torch.equal(a.cdf, b.cdf) and torch.equal(a.data_chunks[0].bytestream, b.data_chunks[0].bytestream)
+    out_v = de_v.from_bytes(blob_v)
+    out_h = de_h.from_bytes(blob_h)
+    assert out_h.dtype == torch.float16 and tuple(out_h.shape) == (L, 2, H, T, D)
+    assert torch.equal(out_v, out_h.permute(0, 1, 3, 2, 4))
+    err = (out_v.float() - kv.float()).abs().max().item()
+    assert 0 < err < kv.float().abs().max().item()
+
+
+@pytest.mark.parametrize("fmt", ["vllm", "huggingface"])
+@pytest.mark.parametrize("chunk_size", [16, 128, 256])
+def test_reference_serde_cases(monkeypatch, fmt, chunk_size):
+    """The reference's own serde tests (LMCache/tests/test_serde.py:27-76): torch.rand KV of 32 layers x
+    8 heads x 128, bf16 for vllm / fp16 for huggingface, Mistral model name (QUANT_LEVEL lookup),
+    chunk sizes 16/128/256 and a chunk 20 tokens short."""
+    monkeypatch.setenv("QUANT_LEVEL", "2")
+    from cachegen_b200.serde.cachegen_basics import CacheGenEncoderOutput
+    model = "mistralai/Mistral-7B-Instruct-v0.2"
+    dtype = torch.bfloat16 if fmt == "vllm" else torch.float16
+    for ntok in (chunk_size, max(1, chunk_size - 20)):
+        shape = [32, 2, ntok, 8, 128] if fmt == "vllm" else [32, 2, 8, ntok, 128]
+        g = torch.Generator(device="cuda").manual_seed(ntok)
+        kv = torch.rand(shape, dtype=dtype, device="cuda", generator=g)
+        ser, de = make_serde(chunk_size, fmt, model=model)
+        blob = ser.to_bytes(kv)
+        eo = CacheGenEncoderOutput.from_bytes(blob)
+        assert eo.num_heads == 8 and eo.head_size == 128
+        decoded = de.from_bytes(blob)
+        de.check_status()
+        assert decoded.shape == kv.shape and decoded.dtype == dtype
+        assert decoded.mean() != 0
+        assert (decoded.float() - kv.float()).abs().max() < 0.2  # rand in [0,1): step is at most 1/7
+    with pytest.raises(RuntimeError, match="chunk_size"):
+        big = torch.rand([32, 2, chunk_size + 1, 8, 128] if fmt == "vllm" else [32, 2, 8, chunk_size + 1, 128],
+                         dtype=dtype, device="cuda")
+        de.from_bytes(ser.to_bytes(big))
+
+
+def test_quality_levels_and_70b_config(oracle):
+    """Half and quarter bin counts (tables of 17 and 9 entries) and the 80-layer configuration."""
+    from cachegen_b200.serde.cachegen_basics import CacheGenConfig
+    from cachegen_b200.synth import generate_kv
+    base = CacheGenConfig.from_model_name(MODEL_7B)
+    for cfg, T in ((base.with_bins_divided(2), 100), (base.with_bins_divided(4), 256)):
+        kv = generate_kv(32, 1, 128, T, seed=cfg.max_bins, device="cpu", dtype=torch.float16)
+        ser, de = make_serde(256, "vllm", cachegen_config=cfg, out_dtype=torch.float16)
+        eo = ser.encode(kv.cuda())
+        assert eo.cdf.shape[2] == cfg.max_bins + 1
+        ref = oracle_encode(oracle, kv, ser.key_bins.cpu().numpy(), ser.value_bins.cpu().numpy(), oracle.F16)
+        assert (eo.cdf.cpu().numpy() == ref["cdf"]).all()
+        assert eo.data_chunks[0].bytestream.cpu().numpy().tobytes() == ref["chunks"][0][0].tobytes()
+        want = oracle.dequantize(ref["sym"].view(np.uint8), ref["bins"], ref["max"], oracle.F16, oracle.F16)
+        assert (bits_np(kv_rows(de.decode(eo))) == want).all()
+    kv = generate_kv(80, 1, 128, 64, seed=3, device="cpu", dtype=torch.float16)
+    ser, de = make_serde(256, "vllm", model="Yukang/LongAlpaca-70B-16k", out_dtype=torch.float16)
+    eo = ser.encode(kv.cuda())
+    ref = oracle_encode(oracle, kv, ser.key_bins.cpu().numpy(), ser.value_bins.cpu().numpy(), oracle.F16)
+    assert eo.data_chunks[0].bytestream.cpu().numpy().tobytes() == ref["chunks"][0][0].tobytes()
+    want = oracle.dequantize(ref["sym"].view(np.uint8), ref["bins"], ref["max"], oracle.F16, oracle.F16)
+    assert (bits_np(kv_rows(de.decode(eo))) == want).all()
+
+
+def test_odd_channel_count_takes_the_scalar_path(oracle):
+    """Head size 20 (not a multiple of 8) and a non-contiguous input."""
+    from cachegen_b200.serde.cachegen_encoder import quantize_and_tables
+    from cachegen_b200.serde.cachegen_basics import CacheGenConfig, make_key_bins, make_value_bins
+    g = torch.Generator().manual_seed(2)
+    L, T, H, D = 32, 40, 3, 20
+    full = torch.randn(L, 2, T, H, D + 4, generator=g).to(torch.float16)
+    kv = full[..., :D]
+    cfg = CacheGenConfig.from_model_name(MODEL_7B)
+    kb, vb = make_key_bins(cfg), make_value_bins(cfg)
+    sym, scales, cdf = quantize_and_tables(kv.cuda(), kb, vb, 32)
+    rows = kv_rows(kv.contiguous())
+    bins = torch.cat((kb, vb)).cpu().numpy()
+    want_sym, want_max = oracle.quantize(bits_np(rows), bins, oracle.F16)
+    assert (sym.cpu().numpy() == want_sym).all()
+    assert (bits_np(scales) == want_max.reshape(2 * L, T)).all()
+    assert (cdf.cpu().numpy() == oracle.calculate_cdf(want_sym, 32)).all()
+
+
+def test_full_size_chunk_properties():
+    """One chunk at the benchmark's full width (32 layers x 32 heads x 128, 256 tokens): encode ->
+    decode -> re-encode is a fixed point, and the decoded values obey the quantiser's error bound."""
+    from cachegen_b200.synth import generate_kv
+    kv = generate_kv(32, 32, 128, 256, seed=1, device="cuda", dtype=torch.float16)
+    ser, de = make_serde(256, "vllm", out_dtype=torch.float16)
+    eo = ser.encode(kv)
+    out = de.decode(eo)
+    de.check_status()
+    eo2 = ser.encode(out)
+    # re-quantising dequantised values with the same per-token maximum reproduces the symbols, so the
+    # second encode must give the same tables and streams whenever the maximum itself is a grid point
+    same = torch.equal(eo2.max_tensors_key, eo.max_tensors_key) and torch.equal(eo2.max_tensors_value, eo.max_tensors_value)
+    assert same
+    assert torch.equal(eo2.cdf, eo.cdf)
+    assert torch.equal(eo2.data_chunks[0].bytestream, eo.data_chunks[0].bytestream)
+    L = 32
+    cq = torch.cat((ser.key_bins, ser.value_bins)).div(2, rounding_mode="floor") - 1
+    step = torch.cat((eo.max_tensors_key, eo.max_tensors_value)).float().reshape(2 * L, 256, 1) / cq[:, None, None]
+    err = (kv_rows(out).float() - kv_rows(kv).float()).abs()
+    assert (err <= 0.5 * step * 1.002 + 1e-6).all()
