@@ -60,8 +60,8 @@ def decode_function_gpu(cdf: torch.Tensor, data_chunks: List[CacheGenGPUBytestre
 
 def _check_chunk(eo: CacheGenGPUEncoderOutput):
     cdf = eo.cdf
-    if not cdf.is_cuda:
-        raise RuntimeError("CDF should be on GPU")
+    if cdf.dim() != 3 or cdf.dtype != torch.int16:
+        raise RuntimeError("CDF must be an int16 tensor [2L, C, Lp]")
     NL, C, lp = cdf.shape
     L = NL // 2
     mk, mv = eo.max_tensors_key, eo.max_tensors_value
@@ -75,6 +75,150 @@ def _check_chunk(eo: CacheGenGPUEncoderOutput):
     return L, C, lp, T
 
 
+def _to_device(t: torch.Tensor, dev) -> torch.Tensor:
+    """Encoded chunks may arrive with their tensors in (pinned) host memory: stage them on `dev`."""
+    if t.device == dev:
+        return t
+    return t.to(dev, non_blocking=True)
+
+
+class DecodePlan:
+    """Everything cg_decode_offsets / cg_decode_dequant need for a list of encoded chunks, built once:
+    device-resident inputs, the job descriptors, the output blob and the launch arguments."""
+
+    def __init__(self, encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Tensor, fmt: str,
+                 out_dtype: torch.dtype, out: torch.Tensor = None, workspace: dict = None, device=None):
+        if not encoder_outputs:
+            raise RuntimeError("nothing to decode")
+        if fmt not in ("vllm", "huggingface"):
+            raise ValueError(f"unknown KV format {fmt!r}")
+        first = encoder_outputs[0]
+        dev = torch.device(device) if device is not None else (
+            first.cdf.device if first.cdf.is_cuda else torch.device("cuda", torch.cuda.current_device()))
+        NL, C, lp = first.cdf.shape
+        L = NL // 2
+        H, D = first.num_heads, first.head_size
+        scale_dtype = first.max_tensors_key.dtype
+        total_T = 0
+        for eo in encoder_outputs:
+            l2, c2, lp2, T = _check_chunk(eo)
+            if (l2, c2, lp2, eo.num_heads, eo.max_tensors_key.dtype) != (L, C, lp, H, scale_dtype):
+                raise RuntimeError("chunks of one decode call must share layers, channels, table length and dtype")
+            total_T += T
+        if bins.numel() != NL:
+            raise RuntimeError(f"bins describe {bins.numel() // 2} layers, the blob has {L}")
+        shape = (L, 2, total_T, H, D) if fmt == "vllm" else (L, 2, H, total_T, D)
+        if out is None:
+            out = torch.empty(shape, dtype=out_dtype, device=dev)
+        elif tuple(out.shape) != shape or out.dtype != out_dtype or out.stride(4) != 1 or out.device != dev:
+            raise RuntimeError("output tensor has the wrong shape, dtype, device or innermost stride")
+        if fmt == "vllm":
+            o_layer, o_kv, o_token, o_head = out.stride(0), out.stride(1), out.stride(2), out.stride(3)
+        else:
+            o_layer, o_kv, o_head, o_token = out.stride(0), out.stride(1), out.stride(2), out.stride(3)
+        nslab = (C + _lib.CG_GROUP_CHANNELS - 1) // _lib.CG_GROUP_CHANNELS
+        ngroups = NL * nslab
+        njobs_total = sum(len(eo.data_chunks) for eo in encoder_outputs)
+        ws = workspace if workspace is not None else {}
+        goff = ws.get("group_off")
+        if goff is None or goff.numel() < njobs_total * ngroups or goff.device != dev:
+            goff = torch.empty(njobs_total * ngroups, dtype=torch.int64, device=dev)
+            ws["group_off"] = goff
+        status = ws.get("status")
+        if status is None or status.device != dev:
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            ws["status"] = status
+
+        esz = out.element_size()
+        self.keep = []  # tensors that must outlive the launches
+        jobs_all = []
+        self.payload_bytes = 0
+        t0 = 0
+        with torch.cuda.device(dev):
+            for eo in encoder_outputs:
+                T = eo.max_tensors_key.shape[1]
+                mk = _to_device(eo.max_tensors_key, dev).reshape(L, T).contiguous()
+                mv = _to_device(eo.max_tensors_value, dev).reshape(L, T).contiguous()
+                cdf = _to_device(eo.cdf, dev).contiguous()
+                self.keep += [mk, mv, cdf]
+                tc = 0
+                for dc in eo.data_chunks:
+                    if dc.bytestream.dtype != torch.uint8 or dc.bytestream.dim() != 1:
+                        raise RuntimeError("bytestream must be a 1-D uint8 tensor")
+                    if dc.bytestream_lengths.dtype != torch.int32 or dc.bytestream_lengths.numel() != NL * C:
+                        raise RuntimeError("bytestream_lengths must be int32 [2L, C]")
+                    if not 0 < dc.ntokens <= CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK:
+                        raise RuntimeError("a sub-chunk holds 1..256 tokens")
+                    bs = _to_device(dc.bytestream, dev).contiguous()
+                    ln = _to_device(dc.bytestream_lengths, dev).contiguous()
+                    self.keep += [bs, ln]
+                    self.payload_bytes += bs.numel()
+                    job = _lib.DecodeJob()
+                    job.cdf = cdf.data_ptr()
+                    job.bytes = bs.data_ptr()
+                    job.lengths = ln.data_ptr()
+                    job.group_off = goff.data_ptr() + 8 * len(jobs_all) * ngroups
+                    job.scales_k = mk.data_ptr() + mk.element_size() * tc
+                    job.scales_v = mv.data_ptr() + mv.element_size() * tc
+                    job.out = out.data_ptr() + esz * (t0 + tc) * o_token
+                    job.nbytes = bs.numel()
+                    job.ntokens = dc.ntokens
+                    job.scale_stride = T
+                    jobs_all.append(job)
+                    tc += dc.ntokens
+                t0 += T
+        self.batches = []
+        for b in range(0, njobs_total, _lib.CG_MAX_DECODE_JOBS):
+            batch = jobs_all[b:b + _lib.CG_MAX_DECODE_JOBS]
+            self.batches.append(((_lib.DecodeJob * len(batch))(*batch), len(batch),
+                                 ctypes.c_void_p(goff.data_ptr() + 8 * b * ngroups)))
+        self.out, self.dev, self.bins, self.status, self.goff = out, dev, bins, status, goff
+        self.dims = (L, H, D, C, lp, NL, total_T)
+        self.strides = (o_layer, o_kv, o_token, o_head)
+        self.dtypes = (_DTYPES[scale_dtype], _DTYPES[out_dtype])
+        self.njobs = njobs_total
+        # bytes one decode pass must move: 16-bit KV out, payload, tables, lengths, scales in
+        self.table_bytes = sum(eo.cdf.numel() * 2 for eo in encoder_outputs)
+        self.length_bytes = njobs_total * NL * C * 4
+        self.scale_bytes = NL * total_T * 2
+        self.output_bytes = NL * total_T * C * esz
+
+    # launches per call: 2 per batch
+    def run_offsets(self) -> None:
+        lib = _lib.lib()
+        L, H, D, C, lp, NL, _ = self.dims
+        with torch.cuda.device(self.dev):
+            st = _stream(self.dev)
+            for arr, n, goff in self.batches:
+                rc = lib.cg_decode_offsets(arr, n, NL, C, goff, ctypes.c_void_p(self.status.data_ptr()), st)
+                _lib.check(rc, "cg_decode_offsets")
+
+    # launches per call: 1 per batch
+    def run_decode(self) -> None:
+        lib = _lib.lib()
+        L, H, D, C, lp, NL, _ = self.dims
+        o_layer, o_kv, o_token, o_head = self.strides
+        with torch.cuda.device(self.dev):
+            st = _stream(self.dev)
+            for arr, n, _ in self.batches:
+                rc = lib.cg_decode_dequant(arr, n, L, H, D, lp, ctypes.c_void_p(self.bins.data_ptr()),
+                                           self.dtypes[0], self.dtypes[1], o_layer, o_kv, o_token, o_head,
+                                           ctypes.c_void_p(self.status.data_ptr()), st)
+                _lib.check(rc, "cg_decode_dequant")
+
+    def run(self) -> torch.Tensor:
+        self.run_offsets()
+        self.run_decode()
+        cur = torch.cuda.current_stream(self.dev)
+        for t in self.keep:
+            t.record_stream(cur)
+        return self.out
+
+    @property
+    def launches(self) -> int:
+        return 3 * len(self.batches)
+
+
 def decode_many(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Tensor, fmt: str,
                 out_dtype: torch.dtype, out: torch.Tensor = None, workspace: dict = None) -> torch.Tensor:
     """Fused decode of consecutive encoded chunks of one KV cache into one blob.
@@ -85,101 +229,12 @@ def decode_many(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Ten
     (LMCache/lmcache/cache_engine.py:282-320 in the reference).  All sub-chunks of all chunks go
     through cg_decode_offsets + cg_decode_dequant in batches of up to 48 per launch.
 
-    bins: float32 [2L] on the GPU (key bins then value bins).  `out`, when given, must have the result's
-    shape and dtype with a unit innermost stride (any other strides).  `workspace` caches the small
-    offset / status buffers between calls.
+    The chunks' tensors may live on the GPU or in (pinned) host memory; host tensors are copied to the
+    GPU on the current stream first.  bins: float32 [2L] on the GPU (key bins then value bins).
+    `out`, when given, must have the result's shape and dtype with a unit innermost stride (any other
+    strides).  `workspace` caches the small offset / status buffers between calls.
     """
-    if not encoder_outputs:
-        raise RuntimeError("nothing to decode")
-    first = encoder_outputs[0]
-    L, C, lp, _ = _check_chunk(first)
-    NL = 2 * L
-    H, D = first.num_heads, first.head_size
-    dev = first.cdf.device
-    scale_dtype = first.max_tensors_key.dtype
-    total_T = 0
-    for eo in encoder_outputs:
-        l2, c2, lp2, T = _check_chunk(eo)
-        if (l2, c2, lp2, eo.num_heads, eo.max_tensors_key.dtype) != (L, C, lp, H, scale_dtype):
-            raise RuntimeError("chunks of one decode call must share layers, channels, table length and dtype")
-        total_T += T
-    if bins.numel() != NL:
-        raise RuntimeError(f"bins describe {bins.numel() // 2} layers, the blob has {L}")
-    shape = (L, 2, total_T, H, D) if fmt == "vllm" else (L, 2, H, total_T, D)
-    if out is None:
-        out = torch.empty(shape, dtype=out_dtype, device=dev)
-    elif tuple(out.shape) != shape or out.dtype != out_dtype or out.stride(4) != 1 or out.device != dev:
-        raise RuntimeError("output tensor has the wrong shape, dtype, device or innermost stride")
-    if fmt == "vllm":
-        o_layer, o_kv, o_token, o_head = out.stride(0), out.stride(1), out.stride(2), out.stride(3)
-    else:
-        o_layer, o_kv, o_head, o_token = out.stride(0), out.stride(1), out.stride(2), out.stride(3)
-
-    nslab = (C + _lib.CG_GROUP_CHANNELS - 1) // _lib.CG_GROUP_CHANNELS
-    ngroups = NL * nslab
-    njobs_total = sum(len(eo.data_chunks) for eo in encoder_outputs)
-    ws = workspace if workspace is not None else {}
-    goff = ws.get("group_off")
-    if goff is None or goff.numel() < njobs_total * ngroups or goff.device != dev:
-        goff = torch.empty(njobs_total * ngroups, dtype=torch.int64, device=dev)
-        ws["group_off"] = goff
-    status = ws.get("status")
-    if status is None or status.device != dev:
-        status = torch.zeros(1, dtype=torch.int32, device=dev)
-        ws["status"] = status
-
-    esz = out.element_size()
-    keep = []  # tensors that must outlive the launches
-    jobs_all = []
-    t0 = 0
-    for eo in encoder_outputs:
-        T = eo.max_tensors_key.shape[1]
-        mk = eo.max_tensors_key.reshape(L, T).contiguous()
-        mv = eo.max_tensors_value.reshape(L, T).contiguous()
-        cdf = eo.cdf.contiguous()
-        keep += [mk, mv, cdf]
-        tc = 0
-        for dc in eo.data_chunks:
-            bs = dc.bytestream.contiguous()
-            ln = dc.bytestream_lengths.contiguous()
-            if ln.dtype != torch.int32 or ln.numel() != NL * C:
-                raise RuntimeError("bytestream_lengths must be int32 [2L, C]")
-            if bs.dtype != torch.uint8 or not bs.is_cuda or not ln.is_cuda:
-                raise RuntimeError("bytestream must be a uint8 CUDA tensor")
-            if not 0 < dc.ntokens <= CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK:
-                raise RuntimeError("a sub-chunk holds 1..256 tokens")
-            keep += [bs, ln]
-            job = _lib.DecodeJob()
-            job.cdf = cdf.data_ptr()
-            job.bytes = bs.data_ptr()
-            job.lengths = ln.data_ptr()
-            job.group_off = goff.data_ptr() + 8 * len(jobs_all) * ngroups
-            job.scales_k = mk.data_ptr() + mk.element_size() * tc
-            job.scales_v = mv.data_ptr() + mv.element_size() * tc
-            job.out = out.data_ptr() + esz * (t0 + tc) * o_token
-            job.nbytes = bs.numel()
-            job.ntokens = dc.ntokens
-            job.scale_stride = T
-            jobs_all.append(job)
-            tc += dc.ntokens
-        t0 += T
-    lib = _lib.lib()
-    with torch.cuda.device(dev):
-        st = _stream(dev)
-        for b in range(0, njobs_total, _lib.CG_MAX_DECODE_JOBS):
-            batch = jobs_all[b:b + _lib.CG_MAX_DECODE_JOBS]
-            arr = (_lib.DecodeJob * len(batch))(*batch)
-            rc = lib.cg_decode_offsets(arr, len(batch), NL, C, ctypes.c_void_p(goff.data_ptr() + 8 * b * ngroups),
-                                       ctypes.c_void_p(status.data_ptr()), st)
-            _lib.check(rc, "cg_decode_offsets")
-            rc = lib.cg_decode_dequant(arr, len(batch), L, H, D, lp, ctypes.c_void_p(bins.data_ptr()),
-                                       _DTYPES[scale_dtype], _DTYPES[out_dtype], o_layer, o_kv, o_token, o_head,
-                                       ctypes.c_void_p(status.data_ptr()), st)
-            _lib.check(rc, "cg_decode_dequant")
-    cur = torch.cuda.current_stream(dev)
-    for t in keep:
-        t.record_stream(cur)
-    return out
+    return DecodePlan(encoder_outputs, bins, fmt, out_dtype, out=out, workspace=workspace).run()
 
 
 def decode_to_kv(encoder_output: CacheGenGPUEncoderOutput, bins: torch.Tensor, fmt: str, out_dtype: torch.dtype,
@@ -218,20 +273,28 @@ class CacheGenDeserializer(Deserializer):
         if ntokens > self.chunk_size:
             # the reference slices a chunk_size-row buffer and fails in its reshape (dec.py:138-141,101)
             raise RuntimeError(f"blob holds {ntokens} tokens, more than chunk_size = {self.chunk_size}")
-        dev = encoder_output.cdf.device
-        if self._bins.device != dev:
-            self._bins = self._bins.to(dev)
-        return decode_to_kv(encoder_output, self._bins, self.fmt, self.out_dtype, out=out, workspace=self._workspace)
+        return decode_to_kv(encoder_output, self._bins_on(encoder_output.cdf.device), self.fmt, self.out_dtype,
+                            out=out, workspace=self._workspace)
 
     def decode_many(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None) -> torch.Tensor:
         """Consecutive chunks of one KV cache into one blob, in as few launches as possible."""
         for eo in encoder_outputs:
             if eo.max_tensors_key.shape[1] > self.chunk_size:
                 raise RuntimeError(f"a blob holds more tokens than chunk_size = {self.chunk_size}")
-        dev = encoder_outputs[0].cdf.device
+        return decode_many(encoder_outputs, self._bins_on(encoder_outputs[0].cdf.device), self.fmt, self.out_dtype,
+                           out=out, workspace=self._workspace)
+
+    def plan(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None) -> DecodePlan:
+        """The launch plan decode_many would run, for callers that decode the same chunks repeatedly."""
+        return DecodePlan(encoder_outputs, self._bins_on(encoder_outputs[0].cdf.device), self.fmt, self.out_dtype,
+                          out=out, workspace=self._workspace)
+
+    def _bins_on(self, dev) -> torch.Tensor:
+        if not dev.type == "cuda":
+            dev = torch.device("cuda", torch.cuda.current_device())
         if self._bins.device != dev:
             self._bins = self._bins.to(dev)
-        return decode_many(encoder_outputs, self._bins, self.fmt, self.out_dtype, out=out, workspace=self._workspace)
+        return self._bins
 
     def check_status(self) -> None:
         """Synchronises and raises if a decode since the last check met malformed stream lengths."""
@@ -243,11 +306,5 @@ class CacheGenDeserializer(Deserializer):
                 raise RuntimeError("cachegen decode: " + _lib.status_text(bits))
 
     def from_bytes(self, bs: bytes) -> torch.Tensor:
-        encoder_output = CacheGenGPUEncoderOutput.from_bytes(bs)
-        encoder_output.cdf = encoder_output.cdf.cuda()
-        encoder_output.max_tensors_key = encoder_output.max_tensors_key.cuda()
-        encoder_output.max_tensors_value = encoder_output.max_tensors_value.cuda()
-        for dc in encoder_output.data_chunks:
-            dc.bytestream = dc.bytestream.cuda()
-            dc.bytestream_lengths = dc.bytestream_lengths.cuda()
-        return self.decode(encoder_output)
+        # tensors pickled on a GPU come back on that GPU; anything else is staged by the decode plan
+        return self.decode(CacheGenGPUEncoderOutput.from_bytes(bs))

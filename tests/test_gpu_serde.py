@@ -183,4 +183,5 @@ def test_full_size_chunk_properties():
     cq = torch.cat((ser.key_bins, ser.value_bins)).div(2, rounding_mode="floor") - 1
     step = torch.cat((eo.max_tensors_key, eo.max_tensors_value)).float().reshape(2 * L, 256, 1) / cq[:, None, None]
     err = (kv_rows(out).float() - kv_rows(kv).float()).abs()
-    assert (err <= 0.5 * step * 1.002 + 1e-6).all()
+    # half a quantisation step, plus the rounding of the result to fp16 (half an ulp at the row maximum)
+    assert (err <= 0.5 * step * 1.001 + step * cq[:, None, None] * 2.0 ** -10 + 1e-6).all()
