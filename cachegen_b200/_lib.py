@@ -3,7 +3,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libcachegen_b200.so")
+# CACHEGEN_B200_LIB selects another build of the library (same ABI), e.g. one kept outside the package
+LIB_PATH = os.environ.get("CACHEGEN_B200_LIB") or os.path.join(_HERE, "libcachegen_b200.so")
 
 CG_F16, CG_BF16 = 0, 1
 CG_MAX_TOKENS_PER_STREAM = 256

@@ -29,15 +29,19 @@ def needs_build():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, extra_flags=(), out=None):
+    """Compiles the library; `extra_flags` (e.g. -D switches) and `out` are for experiments."""
+    global LIB
+    if out:
+        LIB, force = out, True
     if not force and not needs_build():
         return LIB
-    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
+    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")] + list(extra_flags)
     if verbose:
         flags = flags + ["-Xptxas", "-v"]
 
     def one(src):
-        obj = os.path.join(CSRC, src.replace(".cu", ".o"))
+        obj = (out + "." if out else CSRC + os.sep) + src.replace(".cu", ".o")
         cmd = [_nvcc(), "-c", os.path.join(CSRC, src), "-o", obj] + flags
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:

@@ -13,8 +13,8 @@
 //     value - low directly;
 //   * within one symbol the renormalisation loop does a run of "equal top bit" shifts followed
 //     by a run of "underflow" shifts, never the other way round; both run lengths come from a
-//     count-leading-zeros, the decoder's `value` takes all its new bits in one funnel shift and
-//     the encoder emits the shifted-out top bits of `low` in one append.
+//     count-leading-zeros, the decoder takes all its new bits in one funnel shift and the encoder
+//     emits the shifted-out top bits of `low` in one append.
 #pragma once
 
 #include <stdint.h>
@@ -94,115 +94,196 @@ CG_HD int equal_shifts(uint32_t low, uint32_t high) { return cg_clz((low ^ high)
 // low has a 1 and high a 0.
 CG_HD int underflow_shifts(uint32_t low, uint32_t high) { return cg_clz((((~low) | high) << 1) | 1u); }
 
-// ---- table access ---------------------------------------------------------------------------------------
+// ---- shared-memory access --------------------------------------------------------------------------------
 // A stream's table is the column tab[m][tid] = cdf[m] << 16 of a [rows][128] uint32 array, addressed
-// by byte address: entry m of the column starting at `col` is at col + m * kTableRowBytes.  On the
-// device the addresses are shared-memory addresses (bank = lane for every m); on the host they are
-// offsets into a plain array.
-struct TableReader {
+// by byte address: entry m of the column starting at `col` is at col + m * kTableRowBytes.  The
+// stream's bit ring (below) is a column of the same shape.  On the device the addresses are
+// shared-memory addresses (bank = lane for every row); on the host they are offsets into a plain array.
+struct Smem {
 #if defined(__CUDA_ARCH__)
-    __device__ __forceinline__ uint32_t operator()(uint32_t addr) const {
+    __device__ __forceinline__ uint32_t ld(uint32_t addr) const {
         uint32_t v;
         asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
         return v;
     }
+    __device__ __forceinline__ void st(uint32_t addr, uint32_t v) const {
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+    }
 #else
-    const uint8_t *base;
-    uint32_t operator()(uint32_t addr) const { return *reinterpret_cast<const uint32_t *>(base + addr); }
+    uint8_t *base;
+    uint32_t ld(uint32_t addr) const { return *reinterpret_cast<const uint32_t *>(base + addr); }
+    void st(uint32_t addr, uint32_t v) const { *reinterpret_cast<uint32_t *>(base + addr) = v; }
 #endif
 };
 
-// ---- MSB-first bit window over one stream ------------------------------------------------------------
-// The byte array is read as aligned 32-bit words; bits before the stream's first byte are shifted
-// out at start-up and words (or word tails) past its last byte read as zero, which is what the
-// reference sees in its zero-padded staging row (dec_new.cu:229-232).
-struct BitWindow {
-    const uint32_t *wp;  // word holding the stream's first byte
-    uint32_t end_bit;    // bit index, counted from wp, one past the stream's last bit
-    uint32_t hi, lo;     // next unread bits, hi's top bit first
-    int nbits;           // valid bits in hi:lo
-    int next;            // next word to fetch
+// ---- MSB-first bit ring over one stream --------------------------------------------------------------
+// Each thread keeps the next 128 bytes of its stream in a column of shared memory, 32 rows of one
+// big-endian 32-bit word plus a 33rd row that repeats row 0's newest word, so that the two words under
+// any bit position are at [row] and [row + 1] without a wrap test.  The per-symbol read is branch-free;
+// a stream longer than the ring is topped up 16 words at a time once the reader has left the half that
+// is overwritten (0.3 % of the streams of the benchmark workload are longer than 128 bytes).
+//
+// The byte array is read as aligned 32-bit words; bits before the stream's first byte are skipped by
+// the start position and words (or word tails) past its last byte are stored as zero, which is what
+// the reference sees in its zero-padded staging row (dec_new.cu:229-232).
+constexpr int kRingWords = 32;
+constexpr int kRingRows = kRingWords + 1;
 
-    CG_HD uint32_t fetch(int j) const {
-        const uint32_t b0 = static_cast<uint32_t>(j) * 32u;
+struct BitRing {
+    const uint32_t *wp;    // word holding the stream's first byte
+    uint32_t end_bit;      // bit index, counted from wp, one past the stream's last bit
+    uint32_t ring;         // address of this stream's ring column (row 0)
+    uint32_t pos;          // bit index, counted from wp, of the next unread bit
+    uint32_t next_refill;  // reaching this position triggers a top-up
+    uint32_t loaded;       // stream words placed in the ring so far
+
+    CG_HD uint32_t fetch(uint32_t j) const {
+        const uint32_t b0 = j * 32u;
         if (b0 >= end_bit) return 0u;
         uint32_t w = cg_bswap32(cg_load_stream_word(wp + j));
         const uint32_t rem = end_bit - b0;
         if (rem < 32u) w &= 0xFFFFFFFFu << (32u - rem);
         return w;
     }
-    // returns the stream's first 32 bits (the coder's initial `value`, dec_new.cu:257)
-    CG_HD uint32_t open(const uint8_t *p, uint32_t len) {
+    // the 32 bits at the current position
+    CG_HD uint32_t peek(Smem sm) const {
+        const uint32_t a = ring + ((pos << 4) & (static_cast<uint32_t>(kRingWords - 1) * kTableRowBytes));
+        return cg_fshl(sm.ld(a + kTableRowBytes), sm.ld(a), pos);
+    }
+    // fills the ring; returns the stream's first 32 bits (the coder's initial `value`, dec_new.cu:257)
+    CG_HD uint32_t open(Smem sm, const uint8_t *p, uint32_t len, uint32_t ring_col) {
         const uintptr_t a = reinterpret_cast<uintptr_t>(p);
         wp = reinterpret_cast<const uint32_t *>(a & ~static_cast<uintptr_t>(3));
         const uint32_t off = static_cast<uint32_t>(a & 3u) * 8u;
         end_bit = off + len * 8u;
-        const uint32_t w0 = fetch(0), w1 = fetch(1), w2 = fetch(2);
-        const uint32_t value = cg_fshl(w1, w0, off);
-        hi = cg_fshl(w2, w1, off);
-        lo = w2 << off;
-        nbits = 64 - static_cast<int>(off);
-        next = 3;
+        ring = ring_col;
+        for (uint32_t j = 0; j < static_cast<uint32_t>(kRingRows); ++j) sm.st(ring + j * kTableRowBytes, fetch(j));
+        loaded = kRingWords;
+        // a stream that fits the ring never needs a top-up unless a (corrupt) stream is read far past its end
+        next_refill = (end_bit <= static_cast<uint32_t>(kRingRows) * 32u) ? kRingWords * 32u : (kRingWords / 2) * 32u;
+        pos = off;
+        const uint32_t value = peek(sm);
+        pos += 32u;
         return value;
     }
-    // shifts s (< 32) fresh bits into `value`
-    CG_HD uint32_t feed(uint32_t value, int s) {
-        value = cg_fshl(hi, value, static_cast<uint32_t>(s));
-        hi = cg_fshl(lo, hi, static_cast<uint32_t>(s));
-        lo <<= s;
-        nbits -= s;
-        if (nbits <= 32) {
-            const uint32_t w = fetch(next++);
-            hi |= cg_fshr_clamp(w, 0u, static_cast<uint32_t>(nbits));
-            lo = cg_fshl_clamp(0u, w, static_cast<uint32_t>(32 - nbits));
-            nbits += 32;
-        }
-        return value;
+    CG_HD void refill(Smem sm) {
+        do {
+            for (uint32_t r = 0; r < static_cast<uint32_t>(kRingWords / 2); ++r) {
+                const uint32_t j = loaded + r, row = j & static_cast<uint32_t>(kRingWords - 1);
+                const uint32_t w = fetch(j);
+                sm.st(ring + row * kTableRowBytes, w);
+                if (row == 0u) sm.st(ring + kRingWords * kTableRowBytes, w);
+            }
+            loaded += kRingWords / 2;
+        } while (loaded < (pos >> 5) + kRingWords / 2 + 1);
+        next_refill = (loaded - kRingWords / 2) * 32u;
+    }
+    CG_HD void advance(Smem sm, uint32_t s) {
+        pos += s;
+        if (pos >= next_refill) refill(sm);
     }
 };
 
 // ---- decode loop ------------------------------------------------------------------------------------------
+#ifndef CG_DEC_VARIANT
+#define CG_DEC_VARIANT 2
+#endif
+// One search step: candidate entry `IMM` bytes above `a`; take it when (span*cdf) >> 16 <= target.
+template <uint32_t IMM>
+CG_HD uint32_t search_step(Smem sm, uint32_t a, uint32_t spanm1, uint32_t target, uint32_t fullmask) {
+#if defined(__CUDA_ARCH__) && (CG_DEC_VARIANT & 4)
+    // span32 = spanm1 + 1 wraps to 0 for the full range: hi32(span32 * c16) + (c16 when full)
+    asm("{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .u32 c, m, hi;\n\t"
+        "ld.shared.u32 c, [%0+%4];\n\t"
+        "and.b32 m, c, %3;\n\t"
+        "mad.hi.u32 hi, %1, c, m;\n\t"
+        "setp.le.u32 p, hi, %2;\n\t"
+        "@p add.u32 %0, %0, %4;\n\t"
+        "}"
+        : "+r"(a)
+        : "r"(spanm1 + 1u), "r"(target), "r"(fullmask), "n"(IMM));
+    (void)sm;
+    return a;
+#elif defined(__CUDA_ARCH__) && !(CG_DEC_VARIANT & 2)
+    asm("{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .u32 c, lo, hi;\n\t"
+        ".reg .u64 t, c64;\n\t"
+        "ld.shared.u32 c, [%0+%3];\n\t"
+        "cvt.u64.u32 c64, c;\n\t"
+        "mad.wide.u32 t, %1, c, c64;\n\t"
+        "mov.b64 {lo, hi}, t;\n\t"
+        "setp.le.u32 p, hi, %2;\n\t"
+        "@p add.u32 %0, %0, %3;\n\t"
+        "}"
+        : "+r"(a)
+        : "r"(spanm1), "r"(target), "n"(IMM));
+    (void)sm;
+    (void)fullmask;
+    return a;
+#else
+    (void)fullmask;
+    const uint32_t ca = a + IMM;
+    return scale_by_cdf(spanm1, sm.ld(ca)) <= target ? ca : a;
+#endif
+}
+
+template <int B, bool POW2>
+struct Search {
+    static CG_HD uint32_t run(Smem sm, uint32_t a, uint32_t a_max, uint32_t spanm1, uint32_t target,
+                              uint32_t fullmask) {
+        constexpr uint32_t kStep = static_cast<uint32_t>(kTableRowBytes) << B;
+        if (POW2) {
+            a = search_step<kStep>(sm, a, spanm1, target, fullmask);
+        } else {  // candidates above the last symbol are never taken
+            const uint32_t ca = a + kStep;
+            const bool take = (ca <= a_max) && (scale_by_cdf(spanm1, sm.ld(ca <= a_max ? ca : a)) <= target);
+            a = take ? ca : a;
+        }
+        return Search<B - 1, POW2>::run(sm, a, a_max, spanm1, target, fullmask);
+    }
+};
+template <bool POW2>
+struct Search<-1, POW2> {
+    static CG_HD uint32_t run(Smem, uint32_t a, uint32_t, uint32_t, uint32_t, uint32_t) { return a; }
+};
+
 // col: address of the stream's table column; emit(i, m) receives token index and symbol.
 // LEVELS: search depth, 2^LEVELS >= maxsym + 1.  POW2: 2^LEVELS == maxsym + 1, so no candidate can
 // exceed maxsym and the bound check is dropped.
+//
+// State: low, spanm1 = high - low, and offset = value - low.  In this form both kinds of
+// renormalisation shift act alike on the pair (offset, span) -- offset = 2*offset + next bit,
+// span = 2*span -- so the reference's "value -= 2^30" of the underflow case needs no separate step;
+// low is still tracked because the shift counts depend on the bit patterns of low and high.
 template <int LEVELS, bool POW2, class Emit>
-CG_HD void decode_stream(TableReader tab, uint32_t col, int maxsym, BitWindow &bw, uint32_t value, int ntok,
-                         Emit emit) {
-    uint32_t low = 0u, high = 0xFFFFFFFFu;
+CG_HD void decode_stream(Smem sm, uint32_t col, int maxsym, BitRing &bits, uint32_t value, int ntok, Emit emit) {
+    uint32_t low = 0u, spanm1 = 0xFFFFFFFFu, offset = value;
     const uint32_t a_max = col + static_cast<uint32_t>(maxsym) * kTableRowBytes;
     for (int i = 0; i < ntok; ++i) {
-        const uint32_t spanm1 = high - low;
-        const uint32_t target = value - low;
-        // largest m in [0, maxsym] with (span*cdf[m]) >> 16 <= target (binsearch, dec_new.cu:52-71)
-        uint32_t a = col;
-#if defined(__CUDA_ARCH__)
-#pragma unroll
-#endif
-        for (int b = LEVELS - 1; b >= 0; --b) {
-            const uint32_t ca = a + (static_cast<uint32_t>(kTableRowBytes) << b);
-            const uint32_t f = scale_by_cdf(spanm1, tab(ca));
-            bool take = f <= target;
-            if (!POW2) take = take && (ca <= a_max);
-            a = take ? ca : a;
-        }
+        const uint32_t win = bits.peek(sm);  // independent of this symbol's search: issued early
+        // largest m in [0, maxsym] with (span*cdf[m]) >> 16 <= value - low (binsearch, dec_new.cu:52-71)
+        const uint32_t fullmask = (spanm1 == 0xFFFFFFFFu) ? 0xFFFFFFFFu : 0u;
+        const uint32_t a = Search<LEVELS - 1, POW2>::run(sm, col, a_max, spanm1, offset, fullmask);
         emit(i, static_cast<int>((a - col) / kTableRowBytes));
         if (i == ntok - 1) break;  // no range update after the last symbol (dec_new.cu:273-275)
 
-        const uint32_t flo = scale_by_cdf(spanm1, tab(a));
-        const uint32_t fhi = (a == a_max) ? spanm1 + 1u : scale_by_cdf(spanm1, tab(a + kTableRowBytes));
-        high = low + fhi - 1u;
-        low = low + flo;
-        // equal-top-bit shifts, then underflow shifts (dec_new.cu:283-301)
-        const int n1 = equal_shifts(low, high);
-        low <<= n1;
-        high = cg_fshl(0xFFFFFFFFu, high, static_cast<uint32_t>(n1));
-        const int k = underflow_shifts(low, high);
-        low = (low << k) & 0x7FFFFFFFu;
-        high = cg_fshl(0xFFFFFFFFu, high, static_cast<uint32_t>(k)) | 0x80000000u;
-        // k underflow steps of "value -= 2^30; value = value*2 + bit" flip only the top bit of the
-        // shifted value
-        value = bw.feed(value, (n1 + k) & 31);
-        value ^= (k != 0) ? 0x80000000u : 0u;
+        const uint32_t flo = scale_by_cdf(spanm1, sm.ld(a));
+        const uint32_t fhi = (a == a_max) ? spanm1 + 1u : scale_by_cdf(spanm1, sm.ld(a + kTableRowBytes));
+        offset -= flo;
+        low += flo;
+        spanm1 = fhi - flo - 1u;
+        const uint32_t high = low + spanm1;
+        // equal-top-bit shifts, then underflow shifts (dec_new.cu:283-301), applied in one go
+        const uint32_t n1 = static_cast<uint32_t>(equal_shifts(low, high));
+        const uint32_t k = static_cast<uint32_t>(cg_clz(((((~low) | high) << n1) << 1) | 1u));
+        const uint32_t s = (n1 + k) & 31u;  // at most 18 for any strictly increasing table
+        low = (low << s) & 0x7FFFFFFFu;
+        spanm1 = cg_fshl(0xFFFFFFFFu, spanm1, s);
+        offset = cg_fshl(win, offset, s);
+        bits.advance(sm, s);
     }
 }
 
@@ -261,11 +342,11 @@ struct EncoderState {
         pending = 0u;
     }
     // one symbol s in [0, maxsym] (enc_new.cu:257-295)
-    CG_HD void step(TableReader tab, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out) {
+    CG_HD void step(Smem sm, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out) {
         const uint32_t a = col + s * kTableRowBytes;
         const uint32_t spanm1 = high - low;
-        const uint32_t flo = scale_by_cdf(spanm1, tab(a));
-        const uint32_t fhi = (s == maxsym) ? spanm1 + 1u : scale_by_cdf(spanm1, tab(a + kTableRowBytes));
+        const uint32_t flo = scale_by_cdf(spanm1, sm.ld(a));
+        const uint32_t fhi = (s == maxsym) ? spanm1 + 1u : scale_by_cdf(spanm1, sm.ld(a + kTableRowBytes));
         high = low + fhi - 1u;
         low = low + flo;
         // equal-top-bit shifts: their n1 bits are low's top bits; the first is followed by the pending

@@ -47,9 +47,10 @@ __device__ __forceinline__ uint32_t smem_addr(const void *p) {
 // fills (and later reads) only its own column, so no block barrier is needed.
 __device__ __forceinline__ void stage_table_column(uint32_t *tab, const int16_t *cdf_row, int lp,
                                                    int rows, int tid) {
-    for (int m = 0; m < lp; ++m)
+    const int n = lp < rows ? lp : rows;
+    for (int m = 0; m < n; ++m)
         tab[m * kGroup + tid] = static_cast<uint32_t>(static_cast<uint16_t>(__ldg(cdf_row + m))) << 16;
-    for (int m = lp; m < rows; ++m) tab[m * kGroup + tid] = 0u;
+    for (int m = n; m < rows; ++m) tab[m * kGroup + tid] = 0u;
 }
 
 // ---- block-wide exclusive scan over kGroup (=128) ints ------------------------------------------

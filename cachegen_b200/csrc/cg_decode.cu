@@ -6,6 +6,12 @@
 
 namespace cg {
 
+// Rows of a staged table: entries 0 .. lp-2 are searched (the entry after the last symbol stands for
+// 2^16 and is never read), padded up to the span of the search.
+__host__ __device__ inline int table_rows(int lp, int levels) {
+    return (1 << levels) > lp - 1 ? (1 << levels) : lp - 1;
+}
+
 // ---- symbol-output kernels (decode_fast_prefsum / decode_fast_new) -----------------------------------
 struct SymDecodeParams {
     const int16_t *cdf;
@@ -45,13 +51,14 @@ __global__ void __launch_bounds__(kGroup) decode_symbols_kernel(const SymDecodeP
     if (len > (1 << 20)) len = 1 << 20;
     if (bad && p.status) atomicOr(p.status, CG_S_BAD_LENGTHS);
 
-    const int rows = (1 << LEVELS) > p.lp ? (1 << LEVELS) : p.lp;
+    const int rows = table_rows(p.lp, LEVELS);
     stage_table_column(tab, p.cdf + g * p.lp, p.lp, rows, tid);
-    BitWindow bw;
-    const uint32_t value = bw.open(p.bytes + start, static_cast<uint32_t>(len));
+    BitRing bits;
+    const uint32_t value = bits.open(Smem{}, p.bytes + start, static_cast<uint32_t>(len),
+                                     smem_addr(tab + rows * kGroup + tid));
     uint8_t *o = p.out + row * p.o0 + c * p.o2;
     const int64_t o1 = p.o1;
-    decode_stream<LEVELS, POW2>(TableReader{}, smem_addr(tab + tid), p.lp - 2, bw, value, p.ntokens,
+    decode_stream<LEVELS, POW2>(Smem{}, smem_addr(tab + tid), p.lp - 2, bits, value, p.ntokens,
                                 [&](int i, int m) { o[i * o1] = static_cast<uint8_t>(m); });
 }
 
@@ -99,18 +106,24 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
         const float cq = half_range(__ldg(p.bins + row));
         lut[tid] = __fdiv_rn(__fsub_rn(static_cast<float>(tid), cq), cq);
     }
-    const int rows = (1 << LEVELS) > p.lp ? (1 << LEVELS) : p.lp;
+    const int rows = table_rows(p.lp, LEVELS);
     if (active) stage_table_column(smem, job.cdf + g * p.lp, p.lp, rows, tid);
     __syncthreads();
     if (!active) return;
 
-    BitWindow bw;
-    const uint32_t value = bw.open(job.bytes + start, static_cast<uint32_t>(len));
+    BitRing bits;
+    const uint32_t value = bits.open(Smem{}, job.bytes + start, static_cast<uint32_t>(len),
+                                     smem_addr(smem + rows * kGroup + tid));
     const int h = c / p.head_size, d = c - h * p.head_size;
     uint16_t *o = static_cast<uint16_t *>(job.out) + layer * p.o_layer + kv * p.o_kv + h * p.o_head + d;
-    const int64_t o_token = p.o_token;
-    const uint32_t lut_a = smem_addr(lut), sc_a = smem_addr(scale_f);
-    decode_stream<LEVELS, POW2>(TableReader{}, smem_addr(smem + tid), p.lp - 2, bw, value, ntok, [&](int i, int m) {
+    int64_t o_token = p.o_token;
+    uint32_t lut_a = smem_addr(lut), sc_a = smem_addr(scale_f);
+    int ntok_r = ntok;
+#if CG_DEC_VARIANT & 1
+    // keep the loop's invariants in registers instead of re-deriving them from kernel parameters
+    asm volatile("" : "+l"(o_token), "+r"(lut_a), "+r"(sc_a), "+r"(ntok_r));
+#endif
+    decode_stream<LEVELS, POW2>(Smem{}, smem_addr(smem + tid), p.lp - 2, bits, value, ntok_r, [&](int i, int m) {
         // ((sym - Cq) / Cq) * max in fp32, then one round-to-nearest cast (cachegen_decoder.py:30-33,171-173)
         const float v = __fmul_rn(ldsf32(lut_a + 4u * m), ldsf32(sc_a + 4u * i));
         o[i * o_token] = Half16<OUT_DT>::from_float(v);
@@ -118,9 +131,9 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
 }
 
 // ---- launch helpers -------------------------------------------------------------------------------------
+// dynamic shared memory of a decoder block: the streams' tables, then their bit rings
 static size_t table_bytes(int lp, int levels) {
-    const int rows = (1 << levels) > lp ? (1 << levels) : lp;
-    return static_cast<size_t>(rows) * kRowBytes;
+    return static_cast<size_t>(table_rows(lp, levels) + kRingRows) * kRowBytes;
 }
 
 // Instantiated search depths: exact power-of-two tables for lp = 9, 17, 33 and clamped searches of
@@ -130,8 +143,14 @@ static int launch_symbols(const SymDecodeParams &p, int nrows, cudaStream_t st) 
     const int need = search_levels(p.lp);
     const bool pow2 = (1 << need) == p.lp - 1;
     const dim3 grid((p.nchannels + kGroup - 1) / kGroup, nrows), block(kGroup);
-#define CG_LAUNCH_SYM(L, P2) \
-    decode_symbols_kernel<L, P2, MODE><<<grid, block, table_bytes(p.lp, L), st>>>(p)
+#define CG_LAUNCH_SYM(L, P2)                                                                              \
+    do {                                                                                                  \
+        const size_t smem = table_bytes(p.lp, L);                                                         \
+        if (smem > 48 * 1024)                                                                             \
+            cudaFuncSetAttribute(decode_symbols_kernel<L, P2, MODE>,                                      \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));    \
+        decode_symbols_kernel<L, P2, MODE><<<grid, block, smem, st>>>(p);                                 \
+    } while (0)
     if (pow2 && need == 5) CG_LAUNCH_SYM(5, true);
     else if (pow2 && need == 4) CG_LAUNCH_SYM(4, true);
     else if (pow2 && need == 3) CG_LAUNCH_SYM(3, true);
@@ -148,8 +167,14 @@ static int launch_fused(const FusedDecodeParams &p, cudaStream_t st) {
     const int need = search_levels(p.lp);
     const bool pow2 = (1 << need) == p.lp - 1;
     const dim3 grid(p.nslab, 2 * p.nlayers, p.njobs), block(kGroup);
-#define CG_LAUNCH_FUSED(L, P2) \
-    decode_dequant_kernel<L, P2, SCALE_DT, OUT_DT><<<grid, block, table_bytes(p.lp, L), st>>>(p)
+#define CG_LAUNCH_FUSED(L, P2)                                                                            \
+    do {                                                                                                  \
+        const size_t smem = table_bytes(p.lp, L);                                                         \
+        if (smem > 48 * 1024)                                                                             \
+            cudaFuncSetAttribute(decode_dequant_kernel<L, P2, SCALE_DT, OUT_DT>,                          \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));    \
+        decode_dequant_kernel<L, P2, SCALE_DT, OUT_DT><<<grid, block, smem, st>>>(p);                     \
+    } while (0)
     if (pow2 && need == 5) CG_LAUNCH_FUSED(5, true);
     else if (pow2 && need == 4) CG_LAUNCH_FUSED(4, true);
     else if (pow2 && need == 3) CG_LAUNCH_FUSED(3, true);

@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
     const int n = min(kSubTokens, p.ntokens - t0);
     const int maxsym = p.lp - 2;
 
-    stage_table_column(tab, p.cdf + g * p.lp, p.lp, p.lp, tid);
+    stage_table_column(tab, p.cdf + g * p.lp, p.lp, p.lp - 1, tid);
     const uint32_t col = smem_addr(tab + tid);
     const int64_t slot = static_cast<int64_t>(sub) * nrows * p.nchannels + g;
     BitSink out;
@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
             if (base + j >= n) break;
             uint32_t s = buf[j];
             if (s > static_cast<uint32_t>(maxsym)) { s = maxsym; bad_symbol = true; }
-            enc.step(TableReader{}, col, s, static_cast<uint32_t>(maxsym), out);
+            enc.step(Smem{}, col, s, static_cast<uint32_t>(maxsym), out);
         }
     }
     const uint32_t nbytes = enc.flush(out);
@@ -188,7 +188,7 @@ using namespace cg;
 
 static int launch_encode(const EncodeParams &p, int nrows, int nsub, cudaStream_t st) {
     const dim3 grid((p.nchannels + kGroup - 1) / kGroup, nrows, nsub), block(kGroup);
-    encode_kernel<<<grid, block, static_cast<size_t>(p.lp) * kRowBytes, st>>>(p);
+    encode_kernel<<<grid, block, static_cast<size_t>(p.lp - 1) * kRowBytes, st>>>(p);
     return check_launch();
 }
 

@@ -24,8 +24,8 @@ static std::vector<uint32_t> make_table(const uint16_t *cdf, int lp, int rows, i
 
 extern "C" int64_t hm_encode_stream(const uint16_t *cdf, int lp, const int8_t *sym, int n, uint8_t *out,
                                     int64_t cap, int tid) {
-    std::vector<uint32_t> tab = make_table(cdf, lp, lp, tid);
-    TableReader rd{reinterpret_cast<const uint8_t *>(tab.data())};
+    std::vector<uint32_t> tab = make_table(cdf, lp - 1, lp - 1, tid);
+    Smem rd{reinterpret_cast<uint8_t *>(tab.data())};
     const uint32_t col = static_cast<uint32_t>(tid) * 4u;
     BitSink sink;
     sink.init(out, cap);
@@ -37,11 +37,14 @@ extern "C" int64_t hm_encode_stream(const uint16_t *cdf, int lp, const int8_t *s
 
 template <int LEVELS, bool POW2>
 static void run_decode(const uint16_t *cdf, int lp, const uint8_t *bytes, int64_t len, int n, uint8_t *out, int tid) {
-    const int rows = (1 << LEVELS) > lp ? (1 << LEVELS) : lp;
-    std::vector<uint32_t> tab = make_table(cdf, lp, rows, tid);
-    TableReader rd{reinterpret_cast<const uint8_t *>(tab.data())};
-    BitWindow bw;
-    const uint32_t value = bw.open(bytes, static_cast<uint32_t>(len));
+    const int rows = (1 << LEVELS) > lp - 1 ? (1 << LEVELS) : lp - 1;
+    // table rows first, then the stream's bit ring, as in the kernels' shared memory
+    std::vector<uint32_t> tab = make_table(cdf, lp - 1 < rows ? lp - 1 : rows, rows, tid);
+    tab.resize(static_cast<size_t>(rows + kRingRows) * kGroupChannels, 0xDEADBEEFu);
+    Smem rd{reinterpret_cast<uint8_t *>(tab.data())};
+    BitRing bw;
+    const uint32_t ring_col = static_cast<uint32_t>(rows) * kTableRowBytes + static_cast<uint32_t>(tid) * 4u;
+    const uint32_t value = bw.open(rd, bytes, static_cast<uint32_t>(len), ring_col);
     decode_stream<LEVELS, POW2>(rd, static_cast<uint32_t>(tid) * 4u, lp - 2, bw, value, n,
                                 [&](int i, int m) { out[i] = static_cast<uint8_t>(m); });
 }
