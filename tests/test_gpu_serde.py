@@ -79,7 +79,10 @@ def test_formats_agree_and_blobs_round_trip_through_pickle(oracle, fmt):
     blob_v = ser_v.to_bytes(kv)
     kv_h = kv.permute(0, 1, 3, 2, 4).contiguous()
     blob_h = ser_h.to_bytes(kv_h)
-    assert len(blob_v) == len(blob_h)
+    # the reference's test asserts equal lengths (LMCache/tests/test_serde.py:42); pickling a CUDA tensor
+    # goes through torch's legacy storage format, which embeds each storage's address as a decimal
+    # string, so two blobs of identical content can differ by a few bytes
+    assert abs(len(blob_v) - len(blob_h)) <= 64
     a, b = CacheGenEncoderOutput.from_bytes(blob_v), CacheGenEncoderOutput.from_bytes(blob_h)
     assert a.num_heads == H and a.head_size == D
     assert torch.equal(a.cdf, b.cdf) and torch.equal(a.data_chunks[0].bytestream, b.data_chunks[0].bytestream)
