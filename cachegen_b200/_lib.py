@@ -39,8 +39,9 @@ EXPORTS = [
     "cg_version", "cg_status_string", "cg_last_cuda_error",
     "cg_calculate_cdf", "cg_encode_padded", "cg_decode_padded", "cg_decode_prefsum",
     "cg_quantize_cdf", "cg_encode_chunk", "cg_compact_streams",
-    "cg_decode_offsets", "cg_decode_dequant",
+    "cg_decode_offsets", "cg_decode_dequant", "cg_decode_dequant_static",
 ]
+CG_STATIC_OFFSET_ENTRIES = 131072
 
 _lib = None
 
@@ -74,6 +75,7 @@ def lib():
     L.cg_compact_streams.argtypes = [p, i64, p, p, p, i, i, i, p, p]
     L.cg_decode_offsets.argtypes = [ctypes.POINTER(DecodeJob), i, i, i, p, p, p]
     L.cg_decode_dequant.argtypes = [ctypes.POINTER(DecodeJob), i, i, i, i, i, p, i, i, i64, i64, i64, i64, p, p]
+    L.cg_decode_dequant_static.argtypes = L.cg_decode_dequant.argtypes
     for name in EXPORTS:
         fn = getattr(L, name)
         if name not in ("cg_version", "cg_status_string", "cg_last_cuda_error"):

@@ -263,3 +263,56 @@ extern "C" int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int 
     if (scale_dtype == CG_BF16 && out_dtype == CG_F16) return launch_fused<CG_BF16, CG_F16>(p, st);
     return launch_fused<CG_BF16, CG_BF16>(p, st);
 }
+
+// ---- decode without a caller-provided workspace --------------------------------------------------------------
+// Group offsets for callers that cannot allocate (see the header): a fixed array in the library's
+// own device image.  In host code `g_static_group_off` is only a handle for the runtime, not a
+// device address; the address each device gave the array is looked up once per device below.
+static __device__ __align__(256) int64_t g_static_group_off[CG_STATIC_OFFSET_ENTRIES];
+
+#include <mutex>
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+int64_t *g_static_ptr[kMaxDevices];  // device address of g_static_group_off, per device
+
+// Address of the array on the current device; set up on the first call per device.
+int static_group_off(int64_t **out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return set_cuda_error(e);
+    if (dev < 0 || dev >= kMaxDevices) return CG_E_CAPACITY;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void *p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_group_off);
+        if (e != cudaSuccess) return set_cuda_error(e);
+        g_static_ptr[dev] = static_cast<int64_t *>(p);
+    }
+    *out = g_static_ptr[dev];
+    return CG_OK;
+}
+}  // namespace
+
+extern "C" int cg_decode_dequant_static(const cg_decode_job *jobs_host, int njobs, int nlayers, int nheads,
+                                        int head_size, int lp, const float *bins, int scale_dtype,
+                                        int out_dtype, int64_t o_layer, int64_t o_kv, int64_t o_token,
+                                        int64_t o_head, int32_t *status, void *stream) {
+    if (!jobs_host || !bins) return CG_E_NULL;
+    if (njobs <= 0 || nlayers <= 0 || nheads <= 0 || head_size <= 0) return CG_E_SHAPE;
+    if (njobs > CG_MAX_DECODE_JOBS) return CG_E_CAPACITY;
+    const int nchannels = nheads * head_size;
+    const int64_t ngroups = static_cast<int64_t>(2 * nlayers) * ((nchannels + kGroup - 1) / kGroup);
+    if (ngroups * njobs > CG_STATIC_OFFSET_ENTRIES) return CG_E_CAPACITY;
+    int64_t *scratch = nullptr;
+    if (int rc = static_group_off(&scratch)) return rc;
+    cg_decode_job jobs[CG_MAX_DECODE_JOBS];
+    for (int j = 0; j < njobs; ++j) {
+        jobs[j] = jobs_host[j];
+        jobs[j].group_off = scratch + j * ngroups;
+    }
+    if (int rc = cg_decode_offsets(jobs, njobs, 2 * nlayers, nchannels, scratch, status, stream)) return rc;
+    return cg_decode_dequant(jobs, njobs, nlayers, nheads, head_size, lp, bins, scale_dtype, out_dtype,
+                             o_layer, o_kv, o_token, o_head, status, stream);
+}

@@ -218,6 +218,29 @@ int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int nlayers, in
                       int64_t o_layer, int64_t o_kv, int64_t o_token, int64_t o_head,
                       int32_t *status, void *stream);
 
+/*
+ * No counterpart in the reference.  The same work as cg_decode_offsets followed by cg_decode_dequant,
+ * for callers that cannot provide the group-offset workspace because they cannot allocate device
+ * memory where the decode runs: a serving engine that has already handed every free byte of HBM to
+ * its KV block pool, or a latency-critical worker that must keep cudaMalloc (which synchronises the
+ * whole device) off its path.  The offsets live in an array built into the library instead
+ * (CG_STATIC_OFFSET_ENTRIES int64 values, 1 MiB, resident on every GPU that loads the library until
+ * the process exits).
+ *
+ * jobs_host[].group_off is ignored.  Limit: njobs * 2*nlayers * ceil(nheads*head_size / 128) must not
+ * exceed CG_STATIC_OFFSET_ENTRIES, otherwise CG_E_CAPACITY is returned and nothing is launched.
+ * The call allocates nothing.  The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current) and remembers it; make that first call outside
+ * any stream capture.  All calls on a device share the one array and it keeps the previous call's
+ * contents: every entry a call reads it has written first, so nothing needs clearing, but two calls
+ * whose kernels may overlap on the GPU (different streams, no ordering between them) race on it.
+ */
+#define CG_STATIC_OFFSET_ENTRIES 131072
+int cg_decode_dequant_static(const cg_decode_job *jobs_host, int njobs, int nlayers, int nheads,
+                             int head_size, int lp, const float *bins, int scale_dtype, int out_dtype,
+                             int64_t o_layer, int64_t o_kv, int64_t o_token, int64_t o_head,
+                             int32_t *status, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
