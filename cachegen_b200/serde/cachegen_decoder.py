@@ -237,6 +237,56 @@ def decode_many(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Ten
     return DecodePlan(encoder_outputs, bins, fmt, out_dtype, out=out, workspace=workspace).run()
 
 
+_copy_streams = {}
+
+
+def decode_many_pipelined(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Tensor, fmt: str,
+                          out_dtype: torch.dtype, out: torch.Tensor = None, groups: int = 4,
+                          workspaces: list = None) -> torch.Tensor:
+    """decode_many for encoded chunks held in pinned host memory, with the host-to-device copies of
+    one group of chunks overlapped with the decode of the previous group (a copy stream per device;
+    the decode launches stay on the caller's current stream).  `workspaces`: one dict per group."""
+    n = len(encoder_outputs)
+    groups = max(1, min(groups, n))
+    first = encoder_outputs[0]
+    dev = first.cdf.device if first.cdf.is_cuda else torch.device("cuda", torch.cuda.current_device())
+    if groups == 1 or first.cdf.is_cuda:
+        return decode_many(encoder_outputs, bins, fmt, out_dtype, out=out,
+                           workspace=workspaces[0] if workspaces else None)
+    NL, C, _ = first.cdf.shape
+    L, H, D = NL // 2, first.num_heads, first.head_size
+    total_T = sum(eo.max_tensors_key.shape[1] for eo in encoder_outputs)
+    shape = (L, 2, total_T, H, D) if fmt == "vllm" else (L, 2, H, total_T, D)
+    if out is None:
+        out = torch.empty(shape, dtype=out_dtype, device=dev)
+    elif tuple(out.shape) != shape:
+        raise RuntimeError("output tensor has the wrong shape")
+    copy_stream = _copy_streams.get(dev)
+    if copy_stream is None:
+        copy_stream = torch.cuda.Stream(device=dev)
+        _copy_streams[dev] = copy_stream
+    cur = torch.cuda.current_stream(dev)
+    copy_stream.wait_stream(cur)
+    if workspaces is None:
+        workspaces = [dict() for _ in range(groups)]
+    per = (n + groups - 1) // groups
+    t0 = 0
+    for g in range(groups):
+        part = encoder_outputs[g * per:(g + 1) * per]
+        if not part:
+            break
+        tg = sum(eo.max_tensors_key.shape[1] for eo in part)
+        view = out[:, :, t0:t0 + tg] if fmt == "vllm" else out[:, :, :, t0:t0 + tg]
+        with torch.cuda.stream(copy_stream):
+            plan = DecodePlan(part, bins, fmt, out_dtype, out=view, workspace=workspaces[g], device=dev)
+            ready = torch.cuda.Event()
+            ready.record(copy_stream)
+        cur.wait_event(ready)
+        plan.run()
+        t0 += tg
+    return out
+
+
 def decode_to_kv(encoder_output: CacheGenGPUEncoderOutput, bins: torch.Tensor, fmt: str, out_dtype: torch.dtype,
                  out: torch.Tensor = None, workspace: dict = None) -> torch.Tensor:
     """Fused decode of one encoded chunk into its KV blob (see decode_many)."""
@@ -284,6 +334,19 @@ class CacheGenDeserializer(Deserializer):
         return decode_many(encoder_outputs, self._bins_on(encoder_outputs[0].cdf.device), self.fmt, self.out_dtype,
                            out=out, workspace=self._workspace)
 
+    def decode_many_host(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None,
+                         groups: int = 4) -> torch.Tensor:
+        """decode_many for chunks whose tensors sit in pinned host memory: copies and decodes overlap."""
+        ws = self._workspace.setdefault("groups", [dict() for _ in range(groups)])
+        if len(ws) < groups:
+            ws += [dict() for _ in range(groups - len(ws))]
+        return decode_many_pipelined(encoder_outputs, self._bins_on(encoder_outputs[0].cdf.device), self.fmt,
+                                     self.out_dtype, out=out, groups=groups, workspaces=ws)
+
+    def group_status_words(self):
+        """Status words of the pipelined path's per-group workspaces."""
+        return [w["status"] for w in self._workspace.get("groups", []) if "status" in w]
+
     def plan(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None) -> DecodePlan:
         """The launch plan decode_many would run, for callers that decode the same chunks repeatedly."""
         return DecodePlan(encoder_outputs, self._bins_on(encoder_outputs[0].cdf.device), self.fmt, self.out_dtype,
@@ -298,8 +361,8 @@ class CacheGenDeserializer(Deserializer):
 
     def check_status(self) -> None:
         """Synchronises and raises if a decode since the last check met malformed stream lengths."""
-        status = self._workspace.get("status")
-        if status is not None:
+        words = ([self._workspace["status"]] if "status" in self._workspace else []) + self.group_status_words()
+        for status in words:
             bits = int(status.item())
             if bits:
                 status.zero_()
