@@ -188,69 +188,90 @@ struct BitRing {
 #ifndef CG_DEC_VARIANT
 #define CG_DEC_VARIANT 2
 #endif
-// One search step: candidate entry `IMM` bytes above `a`; take it when (span*cdf) >> 16 <= target.
+
+CG_HD uint32_t cg_umulhi(uint32_t a, uint32_t b) {
+#if defined(__CUDA_ARCH__)
+    return __umulhi(a, b);
+#else
+    return static_cast<uint32_t>((static_cast<uint64_t>(a) * b) >> 32);
+#endif
+}
+
+// One step of the fast search: the candidate entry is IMM bytes above `a`; it is taken when
+// hi32(spanm1 * c16) <= target.  That product is the exact (span * c16) >> 32 or one below it (it
+// drops the "+ c16" of scale_by_cdf), so the search can end one entry too high when `target` sits
+// exactly on a boundary; decode_symbol() checks the exact value afterwards.
 template <uint32_t IMM>
-CG_HD uint32_t search_step(Smem sm, uint32_t a, uint32_t spanm1, uint32_t target, uint32_t fullmask) {
-#if defined(__CUDA_ARCH__) && (CG_DEC_VARIANT & 4)
-    // span32 = spanm1 + 1 wraps to 0 for the full range: hi32(span32 * c16) + (c16 when full)
+CG_HD uint32_t search_step_fast(Smem sm, uint32_t a, uint32_t spanm1, uint32_t target) {
+#if defined(__CUDA_ARCH__) && (CG_DEC_VARIANT & 1)
     asm("{\n\t"
         ".reg .pred p;\n\t"
-        ".reg .u32 c, m, hi;\n\t"
-        "ld.shared.u32 c, [%0+%4];\n\t"
-        "and.b32 m, c, %3;\n\t"
-        "mad.hi.u32 hi, %1, c, m;\n\t"
-        "setp.le.u32 p, hi, %2;\n\t"
-        "@p add.u32 %0, %0, %4;\n\t"
-        "}"
-        : "+r"(a)
-        : "r"(spanm1 + 1u), "r"(target), "r"(fullmask), "n"(IMM));
-    (void)sm;
-    return a;
-#elif defined(__CUDA_ARCH__) && !(CG_DEC_VARIANT & 2)
-    asm("{\n\t"
-        ".reg .pred p;\n\t"
-        ".reg .u32 c, lo, hi;\n\t"
-        ".reg .u64 t, c64;\n\t"
+        ".reg .u32 c, h;\n\t"
         "ld.shared.u32 c, [%0+%3];\n\t"
-        "cvt.u64.u32 c64, c;\n\t"
-        "mad.wide.u32 t, %1, c, c64;\n\t"
-        "mov.b64 {lo, hi}, t;\n\t"
-        "setp.le.u32 p, hi, %2;\n\t"
+        "mul.hi.u32 h, %1, c;\n\t"
+        "setp.le.u32 p, h, %2;\n\t"
         "@p add.u32 %0, %0, %3;\n\t"
         "}"
         : "+r"(a)
         : "r"(spanm1), "r"(target), "n"(IMM));
     (void)sm;
-    (void)fullmask;
     return a;
 #else
-    (void)fullmask;
     const uint32_t ca = a + IMM;
-    return scale_by_cdf(spanm1, sm.ld(ca)) <= target ? ca : a;
+    return cg_umulhi(spanm1, sm.ld(ca)) <= target ? ca : a;
 #endif
 }
 
-template <int B, bool POW2>
-struct Search {
-    static CG_HD uint32_t run(Smem sm, uint32_t a, uint32_t a_max, uint32_t spanm1, uint32_t target,
-                              uint32_t fullmask) {
-        constexpr uint32_t kStep = static_cast<uint32_t>(kTableRowBytes) << B;
-        if (POW2) {
-            a = search_step<kStep>(sm, a, spanm1, target, fullmask);
-        } else {  // candidates above the last symbol are never taken
-            const uint32_t ca = a + kStep;
-            const bool take = (ca <= a_max) && (scale_by_cdf(spanm1, sm.ld(ca <= a_max ? ca : a)) <= target);
-            a = take ? ca : a;
-        }
-        return Search<B - 1, POW2>::run(sm, a, a_max, spanm1, target, fullmask);
+template <int B>
+struct FastSearch {
+    static CG_HD uint32_t run(Smem sm, uint32_t a, uint32_t spanm1, uint32_t target) {
+        a = search_step_fast<(static_cast<uint32_t>(kTableRowBytes) << B)>(sm, a, spanm1, target);
+        return FastSearch<B - 1>::run(sm, a, spanm1, target);
     }
 };
-template <bool POW2>
-struct Search<-1, POW2> {
-    static CG_HD uint32_t run(Smem, uint32_t a, uint32_t, uint32_t, uint32_t, uint32_t) { return a; }
+template <>
+struct FastSearch<-1> {
+    static CG_HD uint32_t run(Smem, uint32_t a, uint32_t, uint32_t) { return a; }
 };
 
-// col: address of the stream's table column; emit(i, m) receives token index and symbol.
+// Exact search for tables whose symbol count is not a power of two: candidates above the last symbol
+// are never taken (and never read).
+template <int B>
+struct ClampedSearch {
+    static CG_HD uint32_t run(Smem sm, uint32_t a, uint32_t a_max, uint32_t spanm1, uint32_t target) {
+        const uint32_t ca = a + (static_cast<uint32_t>(kTableRowBytes) << B);
+        const bool ok = ca <= a_max;
+        const bool take = ok && (scale_by_cdf(spanm1, sm.ld(ok ? ca : a)) <= target);
+        return ClampedSearch<B - 1>::run(sm, take ? ca : a, a_max, spanm1, target);
+    }
+};
+template <>
+struct ClampedSearch<-1> {
+    static CG_HD uint32_t run(Smem, uint32_t a, uint32_t, uint32_t, uint32_t) { return a; }
+};
+
+// Address of the table entry of the symbol under `target`, i.e. of the largest m in [0, maxsym] with
+// (span * cdf[m]) >> 16 <= target (binsearch, dec_new.cu:52-71); *flo receives that scaled entry.
+template <int LEVELS, bool POW2>
+CG_HD uint32_t decode_symbol(Smem sm, uint32_t col, uint32_t a_max, uint32_t spanm1, uint32_t target,
+                             uint32_t *flo) {
+    uint32_t a;
+    if (POW2) {
+        a = FastSearch<LEVELS - 1>::run(sm, col, spanm1, target);
+        *flo = scale_by_cdf(spanm1, sm.ld(a));
+        if (*flo > target && a != col) {  // about once in 2^14 symbols
+            a -= kTableRowBytes;
+            *flo = scale_by_cdf(spanm1, sm.ld(a));
+        }
+    } else {
+        a = ClampedSearch<LEVELS - 1>::run(sm, col, a_max, spanm1, target);
+        *flo = scale_by_cdf(spanm1, sm.ld(a));
+    }
+    return a;
+}
+
+// col: address of the stream's table column; emit(i, a) receives the token index and the address of
+// the decoded symbol's table entry (symbol = (a - col) / kTableRowBytes).
 // LEVELS: search depth, 2^LEVELS >= maxsym + 1.  POW2: 2^LEVELS == maxsym + 1, so no candidate can
 // exceed maxsym and the bound check is dropped.
 //
@@ -262,15 +283,11 @@ template <int LEVELS, bool POW2, class Emit>
 CG_HD void decode_stream(Smem sm, uint32_t col, int maxsym, BitRing &bits, uint32_t value, int ntok, Emit emit) {
     uint32_t low = 0u, spanm1 = 0xFFFFFFFFu, offset = value;
     const uint32_t a_max = col + static_cast<uint32_t>(maxsym) * kTableRowBytes;
-    for (int i = 0; i < ntok; ++i) {
+    for (int i = 0; i < ntok - 1; ++i) {
         const uint32_t win = bits.peek(sm);  // independent of this symbol's search: issued early
-        // largest m in [0, maxsym] with (span*cdf[m]) >> 16 <= value - low (binsearch, dec_new.cu:52-71)
-        const uint32_t fullmask = (spanm1 == 0xFFFFFFFFu) ? 0xFFFFFFFFu : 0u;
-        const uint32_t a = Search<LEVELS - 1, POW2>::run(sm, col, a_max, spanm1, offset, fullmask);
-        emit(i, static_cast<int>((a - col) / kTableRowBytes));
-        if (i == ntok - 1) break;  // no range update after the last symbol (dec_new.cu:273-275)
-
-        const uint32_t flo = scale_by_cdf(spanm1, sm.ld(a));
+        uint32_t flo;
+        const uint32_t a = decode_symbol<LEVELS, POW2>(sm, col, a_max, spanm1, offset, &flo);
+        emit(i, a);
         const uint32_t fhi = (a == a_max) ? spanm1 + 1u : scale_by_cdf(spanm1, sm.ld(a + kTableRowBytes));
         offset -= flo;
         low += flo;
@@ -285,6 +302,9 @@ CG_HD void decode_stream(Smem sm, uint32_t col, int maxsym, BitRing &bits, uint3
         offset = cg_fshl(win, offset, s);
         bits.advance(sm, s);
     }
+    // the last symbol: no range update after it (dec_new.cu:273-275)
+    uint32_t flo;
+    emit(ntok - 1, decode_symbol<LEVELS, POW2>(sm, col, a_max, spanm1, offset, &flo));
 }
 
 // ---- MSB-first bit writer into one scratch row (add_bits_to_output, enc_new.cu:21-97) ---------------------

@@ -58,8 +58,10 @@ __global__ void __launch_bounds__(kGroup) decode_symbols_kernel(const SymDecodeP
                                      smem_addr(tab + rows * kGroup + tid));
     uint8_t *o = p.out + row * p.o0 + c * p.o2;
     const int64_t o1 = p.o1;
-    decode_stream<LEVELS, POW2>(Smem{}, smem_addr(tab + tid), p.lp - 2, bits, value, p.ntokens,
-                                [&](int i, int m) { o[i * o1] = static_cast<uint8_t>(m); });
+    const uint32_t col = smem_addr(tab + tid);
+    decode_stream<LEVELS, POW2>(Smem{}, col, p.lp - 2, bits, value, p.ntokens, [&](int i, uint32_t a) {
+        o[i * o1] = static_cast<uint8_t>((a - col) / kRowBytes);
+    });
 }
 
 // ---- fused decode + dequantise + KV-layout store --------------------------------------------------------
@@ -117,15 +119,18 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
     const int h = c / p.head_size, d = c - h * p.head_size;
     uint16_t *o = static_cast<uint16_t *>(job.out) + layer * p.o_layer + kv * p.o_kv + h * p.o_head + d;
     int64_t o_token = p.o_token;
-    uint32_t lut_a = smem_addr(lut), sc_a = smem_addr(scale_f);
+    const uint32_t col = smem_addr(smem + tid);
+    // entry m of the row's (s - Cq)/Cq table is at lut + 4m = lut + (a - col)/128 = (a >> 7) + lut_k,
+    // because a - col is a multiple of 512
+    uint32_t lut_k = smem_addr(lut) - (col >> 7), sc_a = smem_addr(scale_f);
     int ntok_r = ntok;
-#if CG_DEC_VARIANT & 1
+#if CG_DEC_VARIANT & 2
     // keep the loop's invariants in registers instead of re-deriving them from kernel parameters
-    asm volatile("" : "+l"(o_token), "+r"(lut_a), "+r"(sc_a), "+r"(ntok_r));
+    asm volatile("" : "+l"(o_token), "+r"(lut_k), "+r"(sc_a), "+r"(ntok_r));
 #endif
-    decode_stream<LEVELS, POW2>(Smem{}, smem_addr(smem + tid), p.lp - 2, bits, value, ntok_r, [&](int i, int m) {
+    decode_stream<LEVELS, POW2>(Smem{}, col, p.lp - 2, bits, value, ntok_r, [&](int i, uint32_t a) {
         // ((sym - Cq) / Cq) * max in fp32, then one round-to-nearest cast (cachegen_decoder.py:30-33,171-173)
-        const float v = __fmul_rn(ldsf32(lut_a + 4u * m), ldsf32(sc_a + 4u * i));
+        const float v = __fmul_rn(ldsf32((a >> 7) + lut_k), ldsf32(sc_a + 4u * i));
         o[i * o_token] = Half16<OUT_DT>::from_float(v);
     });
 }

@@ -46,7 +46,9 @@ static void run_decode(const uint16_t *cdf, int lp, const uint8_t *bytes, int64_
     const uint32_t ring_col = static_cast<uint32_t>(rows) * kTableRowBytes + static_cast<uint32_t>(tid) * 4u;
     const uint32_t value = bw.open(rd, bytes, static_cast<uint32_t>(len), ring_col);
     decode_stream<LEVELS, POW2>(rd, static_cast<uint32_t>(tid) * 4u, lp - 2, bw, value, n,
-                                [&](int i, int m) { out[i] = static_cast<uint8_t>(m); });
+                                [&](int i, uint32_t a) {
+                                    out[i] = static_cast<uint8_t>((a - static_cast<uint32_t>(tid) * 4u) / kTableRowBytes);
+                                });
 }
 
 // Same dispatch as the kernels' launch helpers.
