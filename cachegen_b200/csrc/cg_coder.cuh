@@ -116,78 +116,21 @@ struct Smem {
 #endif
 };
 
-// ---- MSB-first bit ring over one stream --------------------------------------------------------------
-// Each thread keeps the next 128 bytes of its stream in a column of shared memory, 32 rows of one
-// big-endian 32-bit word plus a 33rd row that repeats row 0's newest word, so that the two words under
-// any bit position are at [row] and [row + 1] without a wrap test.  The per-symbol read is branch-free;
-// a stream longer than the ring is topped up 16 words at a time once the reader has left the half that
-// is overwritten (0.3 % of the streams of the benchmark workload are longer than 128 bytes).
-//
-// The byte array is read as aligned 32-bit words; bits before the stream's first byte are skipped by
-// the start position and words (or word tails) past its last byte are stored as zero, which is what
-// the reference sees in its zero-padded staging row (dec_new.cu:229-232).
-constexpr int kRingWords = 32;
-constexpr int kRingRows = kRingWords + 1;
-
-struct BitRing {
-    const uint32_t *wp;    // word holding the stream's first byte
-    uint32_t end_bit;      // bit index, counted from wp, one past the stream's last bit
-    uint32_t ring;         // address of this stream's ring column (row 0)
-    uint32_t pos;          // bit index, counted from wp, of the next unread bit
-    uint32_t next_refill;  // reaching this position triggers a top-up
-    uint32_t loaded;       // stream words placed in the ring so far
-
-    CG_HD uint32_t fetch(uint32_t j) const {
-        const uint32_t b0 = j * 32u;
-        if (b0 >= end_bit) return 0u;
-        uint32_t w = cg_bswap32(cg_load_stream_word(wp + j));
-        const uint32_t rem = end_bit - b0;
-        if (rem < 32u) w &= 0xFFFFFFFFu << (32u - rem);
-        return w;
-    }
-    // the 32 bits at the current position
-    CG_HD uint32_t peek(Smem sm) const {
-        const uint32_t a = ring + ((pos << 4) & (static_cast<uint32_t>(kRingWords - 1) * kTableRowBytes));
-        return cg_fshl(sm.ld(a + kTableRowBytes), sm.ld(a), pos);
-    }
-    // fills the ring; returns the stream's first 32 bits (the coder's initial `value`, dec_new.cu:257)
-    CG_HD uint32_t open(Smem sm, const uint8_t *p, uint32_t len, uint32_t ring_col) {
-        const uintptr_t a = reinterpret_cast<uintptr_t>(p);
-        wp = reinterpret_cast<const uint32_t *>(a & ~static_cast<uintptr_t>(3));
-        const uint32_t off = static_cast<uint32_t>(a & 3u) * 8u;
-        end_bit = off + len * 8u;
-        ring = ring_col;
-        for (uint32_t j = 0; j < static_cast<uint32_t>(kRingRows); ++j) sm.st(ring + j * kTableRowBytes, fetch(j));
-        loaded = kRingWords;
-        // a stream that fits the ring never needs a top-up unless a (corrupt) stream is read far past its end
-        next_refill = (end_bit <= static_cast<uint32_t>(kRingRows) * 32u) ? kRingWords * 32u : (kRingWords / 2) * 32u;
-        pos = off;
-        const uint32_t value = peek(sm);
-        pos += 32u;
-        return value;
-    }
-    CG_HD void refill(Smem sm) {
-        do {
-            for (uint32_t r = 0; r < static_cast<uint32_t>(kRingWords / 2); ++r) {
-                const uint32_t j = loaded + r, row = j & static_cast<uint32_t>(kRingWords - 1);
-                const uint32_t w = fetch(j);
-                sm.st(ring + row * kTableRowBytes, w);
-                if (row == 0u) sm.st(ring + kRingWords * kTableRowBytes, w);
-            }
-            loaded += kRingWords / 2;
-        } while (loaded < (pos >> 5) + kRingWords / 2 + 1);
-        next_refill = (loaded - kRingWords / 2) * 32u;
-    }
-    CG_HD void advance(Smem sm, uint32_t s) {
-        pos += s;
-        if (pos >= next_refill) refill(sm);
-    }
-};
-
-// ---- decode loop ------------------------------------------------------------------------------------------
-#ifndef CG_DEC_VARIANT
-#define CG_DEC_VARIANT 2
+// ---- register bit window + warp-synchronous refill -----------------------------------------------------------
+// The next 96 unread bits of the stream live in three registers.  The byte array is read as aligned
+// 32-bit words; bits before the stream's first byte are shifted out at start-up and words (or word
+// tails) past its last byte read as zero, which is what the reference sees in its zero-padded staging
+// row (dec_new.cu:229-232).  A refill is taken by the whole warp as soon as any of its lanes is down to
+// 32 bits and tops every lane up past 64 bits, so the refill code runs once per warp every few
+// symbols instead of once per lane.
+CG_HD bool cg_any_lane(uint32_t lanes, bool pred) {
+#if defined(__CUDA_ARCH__)
+    return __any_sync(lanes, pred) != 0;
+#else
+    (void)lanes;
+    return pred;
 #endif
+}
 
 CG_HD uint32_t cg_umulhi(uint32_t a, uint32_t b) {
 #if defined(__CUDA_ARCH__)
@@ -197,36 +140,75 @@ CG_HD uint32_t cg_umulhi(uint32_t a, uint32_t b) {
 #endif
 }
 
-// One step of the fast search: the candidate entry is IMM bytes above `a`; it is taken when
-// hi32(spanm1 * c16) <= target.  That product is the exact (span * c16) >> 32 or one below it (it
-// drops the "+ c16" of scale_by_cdf), so the search can end one entry too high when `target` sits
-// exactly on a boundary; decode_symbol() checks the exact value afterwards.
-template <uint32_t IMM>
-CG_HD uint32_t search_step_fast(Smem sm, uint32_t a, uint32_t spanm1, uint32_t target) {
-#if defined(__CUDA_ARCH__) && (CG_DEC_VARIANT & 1)
-    asm("{\n\t"
-        ".reg .pred p;\n\t"
-        ".reg .u32 c, h;\n\t"
-        "ld.shared.u32 c, [%0+%3];\n\t"
-        "mul.hi.u32 h, %1, c;\n\t"
-        "setp.le.u32 p, h, %2;\n\t"
-        "@p add.u32 %0, %0, %3;\n\t"
-        "}"
-        : "+r"(a)
-        : "r"(spanm1), "r"(target), "n"(IMM));
-    (void)sm;
-    return a;
-#else
-    const uint32_t ca = a + IMM;
-    return cg_umulhi(spanm1, sm.ld(ca)) <= target ? ca : a;
-#endif
-}
+struct BitWindow {
+    const uint32_t *wp;    // word holding the stream's first byte
+    uint32_t end_bit;      // bit index, counted from wp, one past the stream's last bit
+    uint32_t next;         // next word to fetch
+    uint32_t hi, mid, lo;  // unread bits, hi's top bit first
+    int nbits;             // valid bits in hi:mid:lo
 
+    CG_HD uint32_t fetch(uint32_t j) const {
+        const uint32_t b0 = j * 32u;
+        if (b0 >= end_bit) return 0u;
+        uint32_t w = cg_bswap32(cg_load_stream_word(wp + j));
+        const uint32_t rem = end_bit - b0;
+        if (rem < 32u) w &= 0xFFFFFFFFu << (32u - rem);
+        return w;
+    }
+    // returns the stream's first 32 bits (the coder's initial `value`, dec_new.cu:257)
+    CG_HD uint32_t open(const uint8_t *p, uint32_t len) {
+        const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+        wp = reinterpret_cast<const uint32_t *>(a & ~static_cast<uintptr_t>(3));
+        const uint32_t off = static_cast<uint32_t>(a & 3u) * 8u;
+        end_bit = off + len * 8u;
+        const uint32_t w0 = fetch(0), w1 = fetch(1), w2 = fetch(2), w3 = fetch(3);
+        hi = cg_fshl(w2, w1, off);
+        mid = cg_fshl(w3, w2, off);
+        lo = w3 << off;
+        nbits = 96 - static_cast<int>(off);
+        next = 4;
+        return cg_fshl(w1, w0, off);
+    }
+    // drops the s (< 32) bits just shifted into the coder's value
+    CG_HD void consume(uint32_t s) {
+        hi = cg_fshl(mid, hi, s);
+        mid = cg_fshl(lo, mid, s);
+        lo <<= s;
+        nbits -= static_cast<int>(s);
+    }
+    CG_HD bool low_water() const { return nbits <= 32; }
+    CG_HD void refill() {
+        while (nbits <= 64) {
+            const uint32_t w = fetch(next++);
+            const uint32_t p = static_cast<uint32_t>(nbits < 0 ? 0 : nbits);  // nothing valid below position p
+            if (p < 32u) {
+                hi |= cg_fshr_clamp(w, 0u, p);
+                mid |= cg_fshl_clamp(0u, w, 32u - p);
+            } else {
+                mid |= cg_fshr_clamp(w, 0u, p - 32u);
+                lo |= cg_fshl_clamp(0u, w, 64u - p);
+            }
+            nbits = static_cast<int>(p) + 32;
+        }
+    }
+};
+
+// ---- decode loop ------------------------------------------------------------------------------------------
+#ifndef CG_DEC_VARIANT
+#define CG_DEC_VARIANT 0
+#endif
+
+// Scaled table entry for the current span: (span * c16) >> 32 with span32 = span mod 2^32, which is 0
+// exactly when the range is the full 2^32 (then the product is c16 itself).
+CG_HD uint32_t scale_exact(uint32_t span32, uint32_t c16) { return span32 ? cg_umulhi(span32, c16) : c16; }
+
+// Search steps of the fast path (span32 != 0): the candidate entry is IMM bytes above `a`.
 template <int B>
 struct FastSearch {
-    static CG_HD uint32_t run(Smem sm, uint32_t a, uint32_t spanm1, uint32_t target) {
-        a = search_step_fast<(static_cast<uint32_t>(kTableRowBytes) << B)>(sm, a, spanm1, target);
-        return FastSearch<B - 1>::run(sm, a, spanm1, target);
+    static CG_HD uint32_t run(Smem sm, uint32_t a, uint32_t span32, uint32_t target) {
+        const uint32_t ca = a + (static_cast<uint32_t>(kTableRowBytes) << B);
+        a = cg_umulhi(span32, sm.ld(ca)) <= target ? ca : a;
+        return FastSearch<B - 1>::run(sm, a, span32, target);
     }
 };
 template <>
@@ -234,77 +216,110 @@ struct FastSearch<-1> {
     static CG_HD uint32_t run(Smem, uint32_t a, uint32_t, uint32_t) { return a; }
 };
 
-// Exact search for tables whose symbol count is not a power of two: candidates above the last symbol
-// are never taken (and never read).
+// Exact, clamped search: any table length, any span; candidates above the last symbol are never taken
+// (and never read).
 template <int B>
-struct ClampedSearch {
-    static CG_HD uint32_t run(Smem sm, uint32_t a, uint32_t a_max, uint32_t spanm1, uint32_t target) {
+struct ExactSearch {
+    static CG_HD uint32_t run(Smem sm, uint32_t a, uint32_t a_max, uint32_t span32, uint32_t target) {
         const uint32_t ca = a + (static_cast<uint32_t>(kTableRowBytes) << B);
         const bool ok = ca <= a_max;
-        const bool take = ok && (scale_by_cdf(spanm1, sm.ld(ok ? ca : a)) <= target);
-        return ClampedSearch<B - 1>::run(sm, take ? ca : a, a_max, spanm1, target);
+        const bool take = ok && (scale_exact(span32, sm.ld(ok ? ca : a)) <= target);
+        return ExactSearch<B - 1>::run(sm, take ? ca : a, a_max, span32, target);
     }
 };
 template <>
-struct ClampedSearch<-1> {
+struct ExactSearch<-1> {
     static CG_HD uint32_t run(Smem, uint32_t a, uint32_t, uint32_t, uint32_t) { return a; }
 };
 
-// Address of the table entry of the symbol under `target`, i.e. of the largest m in [0, maxsym] with
-// (span * cdf[m]) >> 16 <= target (binsearch, dec_new.cu:52-71); *flo receives that scaled entry.
-template <int LEVELS, bool POW2>
-CG_HD uint32_t decode_symbol(Smem sm, uint32_t col, uint32_t a_max, uint32_t spanm1, uint32_t target,
-                             uint32_t *flo) {
-    uint32_t a;
-    if (POW2) {
-        a = FastSearch<LEVELS - 1>::run(sm, col, spanm1, target);
-        *flo = scale_by_cdf(spanm1, sm.ld(a));
-        if (*flo > target && a != col) {  // about once in 2^14 symbols
-            a -= kTableRowBytes;
-            *flo = scale_by_cdf(spanm1, sm.ld(a));
-        }
-    } else {
-        a = ClampedSearch<LEVELS - 1>::run(sm, col, a_max, spanm1, target);
-        *flo = scale_by_cdf(spanm1, sm.ld(a));
-    }
-    return a;
-}
+// The decoder's arithmetic state: low, span32 = (high - low + 1) mod 2^32 and offset = value - low.
+// In this form both kinds of renormalisation shift act alike on the pair (offset, span) --
+// offset = 2*offset + next bit, span = 2*span -- so the reference's "value -= 2^30" of the underflow
+// case needs no separate step; low is still tracked because the shift counts depend on the bit
+// patterns of low and high.
+struct DecoderState {
+    uint32_t low, span32, offset;
 
-// col: address of the stream's table column; emit(i, a) receives the token index and the address of
-// the decoded symbol's table entry (symbol = (a - col) / kTableRowBytes).
-// LEVELS: search depth, 2^LEVELS >= maxsym + 1.  POW2: 2^LEVELS == maxsym + 1, so no candidate can
-// exceed maxsym and the bound check is dropped.
-//
-// State: low, spanm1 = high - low, and offset = value - low.  In this form both kinds of
-// renormalisation shift act alike on the pair (offset, span) -- offset = 2*offset + next bit,
-// span = 2*span -- so the reference's "value -= 2^30" of the underflow case needs no separate step;
-// low is still tracked because the shift counts depend on the bit patterns of low and high.
-template <int LEVELS, bool POW2, class Emit>
-CG_HD void decode_stream(Smem sm, uint32_t col, int maxsym, BitRing &bits, uint32_t value, int ntok, Emit emit) {
-    uint32_t low = 0u, spanm1 = 0xFFFFFFFFu, offset = value;
-    const uint32_t a_max = col + static_cast<uint32_t>(maxsym) * kTableRowBytes;
-    for (int i = 0; i < ntok - 1; ++i) {
-        const uint32_t win = bits.peek(sm);  // independent of this symbol's search: issued early
-        uint32_t flo;
-        const uint32_t a = decode_symbol<LEVELS, POW2>(sm, col, a_max, spanm1, offset, &flo);
-        emit(i, a);
-        const uint32_t fhi = (a == a_max) ? spanm1 + 1u : scale_by_cdf(spanm1, sm.ld(a + kTableRowBytes));
+    // range update for the symbol whose scaled bounds are [flo, fhi), then renormalisation
+    // (dec_new.cu:277-301): equal-top-bit shifts and underflow shifts applied in one go
+    CG_HD void update(uint32_t flo, uint32_t fhi, BitWindow &bw) {
         offset -= flo;
         low += flo;
-        spanm1 = fhi - flo - 1u;
-        const uint32_t high = low + spanm1;
-        // equal-top-bit shifts, then underflow shifts (dec_new.cu:283-301), applied in one go
+        span32 = fhi - flo;
+        const uint32_t high = low + span32 - 1u;
         const uint32_t n1 = static_cast<uint32_t>(equal_shifts(low, high));
         const uint32_t k = static_cast<uint32_t>(cg_clz(((((~low) | high) << n1) << 1) | 1u));
         const uint32_t s = (n1 + k) & 31u;  // at most 18 for any strictly increasing table
         low = (low << s) & 0x7FFFFFFFu;
-        spanm1 = cg_fshl(0xFFFFFFFFu, spanm1, s);
-        offset = cg_fshl(win, offset, s);
-        bits.advance(sm, s);
+        span32 <<= s;
+        offset = cg_fshl(bw.hi, offset, s);
+        bw.consume(s);
     }
-    // the last symbol: no range update after it (dec_new.cu:273-275)
-    uint32_t flo;
-    emit(ntok - 1, decode_symbol<LEVELS, POW2>(sm, col, a_max, spanm1, offset, &flo));
+};
+
+// One stream.  col: address of the stream's table column, entries cdf << 16, rows kTableRowBytes apart,
+// one readable row past the last symbol's; emit(a) receives, token after token, the address of the
+// decoded symbol's table entry (symbol = (a - col) / kTableRowBytes).  lanes: the warp's lanes that
+// run this loop together (they must all have the same ntok).
+// LEVELS: search depth, 2^LEVELS >= maxsym + 1.  POW2: 2^LEVELS == maxsym + 1 (with LEVELS >= 3): the
+// middle symbols then take the fast path -- entries of the first two search levels in registers,
+// no bound checks, one multiply-high per step -- and leave it only for a symbol that starts from the
+// full 2^32 range (the first one, and about never again), which the exact path decodes.
+template <int LEVELS, bool POW2, class Emit>
+CG_HD void decode_stream(Smem sm, uint32_t col, int maxsym, const uint8_t *stream, uint32_t len, int ntok,
+                         uint32_t lanes, Emit emit) {
+    BitWindow bw;
+    DecoderState st;
+    st.low = 0u;
+    st.span32 = 0u;
+    st.offset = bw.open(stream, len);
+    const uint32_t a_max = col + static_cast<uint32_t>(maxsym) * kTableRowBytes;
+
+    // exact step; with_update = false for the last symbol (dec_new.cu:273-275)
+    auto exact_step = [&](bool with_update) {
+        const uint32_t a = ExactSearch<LEVELS - 1>::run(sm, col, a_max, st.span32, st.offset);
+        emit(a);
+        if (with_update) {
+            const uint32_t flo = scale_exact(st.span32, sm.ld(a));
+            const uint32_t fhi = (a == a_max) ? st.span32 : scale_exact(st.span32, sm.ld(a + kTableRowBytes));
+            st.update(flo, fhi, bw);
+        }
+    };
+
+    constexpr bool kFast = POW2 && LEVELS >= 3;
+    constexpr uint32_t kTop = static_cast<uint32_t>(kTableRowBytes) << (LEVELS > 0 ? LEVELS - 1 : 0);
+    constexpr uint32_t kHalf = kTop >> 1;
+    uint32_t r_mid = 0u, r_lo = 0u, r_hi = 0u;
+    if (kFast) {
+        r_mid = sm.ld(col + kTop);
+        r_lo = sm.ld(col + kHalf);
+        r_hi = sm.ld(col + kTop + kHalf);
+    }
+#if defined(__CUDA_ARCH__) && (CG_DEC_VARIANT & 2)
+#pragma unroll 2
+#endif
+    for (int left = ntok - 1; left > 0; --left) {
+        // rare, and taken by the whole warp: a lane is low on bits, or starts this symbol from the full range
+        if (cg_any_lane(lanes, bw.low_water() || (kFast && st.span32 == 0u)) || !kFast) {
+            if (cg_any_lane(lanes, bw.low_water())) bw.refill();
+            if (!kFast || cg_any_lane(lanes, st.span32 == 0u)) {
+                exact_step(true);
+                continue;
+            }
+        }
+        // levels 1 and 2 from registers, the rest from the table column
+        const bool t1 = cg_umulhi(st.span32, r_mid) <= st.offset;
+        uint32_t a = t1 ? col + kTop : col;
+        const bool t2 = cg_umulhi(st.span32, t1 ? r_hi : r_lo) <= st.offset;
+        a = t2 ? a + kHalf : a;
+        a = FastSearch<(kFast ? LEVELS - 3 : -1)>::run(sm, a, st.span32, st.offset);
+        emit(a);
+        const uint32_t flo = cg_umulhi(st.span32, sm.ld(a));
+        const uint32_t fnext = cg_umulhi(st.span32, sm.ld(a + kTableRowBytes));
+        st.update(flo, (a == a_max) ? st.span32 : fnext, bw);
+    }
+    if (cg_any_lane(lanes, bw.low_water())) bw.refill();
+    exact_step(false);
 }
 
 // ---- MSB-first bit writer into one scratch row (add_bits_to_output, enc_new.cu:21-97) ---------------------

@@ -53,15 +53,15 @@ __global__ void __launch_bounds__(kGroup) decode_symbols_kernel(const SymDecodeP
 
     const int rows = table_rows(p.lp, LEVELS);
     stage_table_column(tab, p.cdf + g * p.lp, p.lp, rows, tid);
-    BitRing bits;
-    const uint32_t value = bits.open(Smem{}, p.bytes + start, static_cast<uint32_t>(len),
-                                     smem_addr(tab + rows * kGroup + tid));
     uint8_t *o = p.out + row * p.o0 + c * p.o2;
     const int64_t o1 = p.o1;
     const uint32_t col = smem_addr(tab + tid);
-    decode_stream<LEVELS, POW2>(Smem{}, col, p.lp - 2, bits, value, p.ntokens, [&](int i, uint32_t a) {
-        o[i * o1] = static_cast<uint8_t>((a - col) / kRowBytes);
-    });
+    auto emit = [&](uint32_t a) {
+        *o = static_cast<uint8_t>((a - col) / kRowBytes);
+        o += o1;
+    };
+    decode_stream<LEVELS, POW2>(Smem{}, col, p.lp - 2, p.bytes + start, static_cast<uint32_t>(len), p.ntokens,
+                                __activemask(), emit);
 }
 
 // ---- fused decode + dequantise + KV-layout store --------------------------------------------------------
@@ -113,9 +113,6 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
     __syncthreads();
     if (!active) return;
 
-    BitRing bits;
-    const uint32_t value = bits.open(Smem{}, job.bytes + start, static_cast<uint32_t>(len),
-                                     smem_addr(smem + rows * kGroup + tid));
     const int h = c / p.head_size, d = c - h * p.head_size;
     uint16_t *o = static_cast<uint16_t *>(job.out) + layer * p.o_layer + kv * p.o_kv + h * p.o_head + d;
     int64_t o_token = p.o_token;
@@ -124,21 +121,25 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
     // because a - col is a multiple of 512
     uint32_t lut_k = smem_addr(lut) - (col >> 7), sc_a = smem_addr(scale_f);
     int ntok_r = ntok;
-#if CG_DEC_VARIANT & 2
+#if !(CG_DEC_VARIANT & 1)
     // keep the loop's invariants in registers instead of re-deriving them from kernel parameters
     asm volatile("" : "+l"(o_token), "+r"(lut_k), "+r"(sc_a), "+r"(ntok_r));
 #endif
-    decode_stream<LEVELS, POW2>(Smem{}, col, p.lp - 2, bits, value, ntok_r, [&](int i, uint32_t a) {
+    auto emit = [&](uint32_t a) {
         // ((sym - Cq) / Cq) * max in fp32, then one round-to-nearest cast (cachegen_decoder.py:30-33,171-173)
-        const float v = __fmul_rn(ldsf32((a >> 7) + lut_k), ldsf32(sc_a + 4u * i));
-        o[i * o_token] = Half16<OUT_DT>::from_float(v);
-    });
+        const float v = __fmul_rn(ldsf32((a >> 7) + lut_k), ldsf32(sc_a));
+        *o = Half16<OUT_DT>::from_float(v);
+        o += o_token;
+        sc_a += 4u;
+    };
+    decode_stream<LEVELS, POW2>(Smem{}, col, p.lp - 2, job.bytes + start, static_cast<uint32_t>(len), ntok_r,
+                                __activemask(), emit);
 }
 
 // ---- launch helpers -------------------------------------------------------------------------------------
-// dynamic shared memory of a decoder block: the streams' tables, then their bit rings
+// dynamic shared memory of a decoder block: the streams' table columns
 static size_t table_bytes(int lp, int levels) {
-    return static_cast<size_t>(table_rows(lp, levels) + kRingRows) * kRowBytes;
+    return static_cast<size_t>(table_rows(lp, levels) + 1) * kRowBytes;  // +1: the row read past the last symbol
 }
 
 // Instantiated search depths: exact power-of-two tables for lp = 9, 17, 33 and clamped searches of

@@ -36,24 +36,21 @@ extern "C" int64_t hm_encode_stream(const uint16_t *cdf, int lp, const int8_t *s
 }
 
 template <int LEVELS, bool POW2>
-static void run_decode(const uint16_t *cdf, int lp, const uint8_t *bytes, int64_t len, int n, uint8_t *out, int tid) {
+static void run_decode(const uint16_t *cdf, int lp, const uint8_t *bytes, int64_t len, int n, uint8_t *out,
+                              int tid) {
     const int rows = (1 << LEVELS) > lp - 1 ? (1 << LEVELS) : lp - 1;
-    // table rows first, then the stream's bit ring, as in the kernels' shared memory
     std::vector<uint32_t> tab = make_table(cdf, lp - 1 < rows ? lp - 1 : rows, rows, tid);
-    tab.resize(static_cast<size_t>(rows + kRingRows) * kGroupChannels, 0xDEADBEEFu);
+    tab.resize(static_cast<size_t>(rows + 1) * kGroupChannels, 0xDEADBEEFu);
     Smem rd{reinterpret_cast<uint8_t *>(tab.data())};
-    BitRing bw;
-    const uint32_t ring_col = static_cast<uint32_t>(rows) * kTableRowBytes + static_cast<uint32_t>(tid) * 4u;
-    const uint32_t value = bw.open(rd, bytes, static_cast<uint32_t>(len), ring_col);
-    decode_stream<LEVELS, POW2>(rd, static_cast<uint32_t>(tid) * 4u, lp - 2, bw, value, n,
-                                [&](int i, uint32_t a) {
-                                    out[i] = static_cast<uint8_t>((a - static_cast<uint32_t>(tid) * 4u) / kTableRowBytes);
-                                });
+    decode_stream<LEVELS, POW2>(rd, static_cast<uint32_t>(tid) * 4u, lp - 2, bytes, static_cast<uint32_t>(len),
+                                       n, 0xFFFFFFFFu, [&](uint32_t a) {
+                                           *out++ = static_cast<uint8_t>((a - static_cast<uint32_t>(tid) * 4u) /
+                                                                         kTableRowBytes);
+                                       });
 }
 
-// Same dispatch as the kernels' launch helpers.
 extern "C" void hm_decode_stream(const uint16_t *cdf, int lp, const uint8_t *bytes, int64_t len, int n,
-                                 uint8_t *out, int tid) {
+                                        uint8_t *out, int tid) {
     const int need = search_levels(lp);
     const bool pow2 = (1 << need) == lp - 1;
     if (pow2 && need == 5) run_decode<5, true>(cdf, lp, bytes, len, n, out, tid);
@@ -64,3 +61,4 @@ extern "C" void hm_decode_stream(const uint16_t *cdf, int lp, const uint8_t *byt
     else if (need == 5) run_decode<5, false>(cdf, lp, bytes, len, n, out, tid);
     else run_decode<6, false>(cdf, lp, bytes, len, n, out, tid);
 }
+
