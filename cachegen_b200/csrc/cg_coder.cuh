@@ -80,20 +80,9 @@ CG_HD uint32_t cg_load_stream_word(const uint32_t *p) {
 #endif
 }
 
-// upper 32 bits of span * c16 where span = spanm1 + 1 (span may be 2^32) and c16 = cdf << 16:
-// equals the (span * cdf) >> 16 of the range update (enc_new.cu:262-263), without the 64-bit shift.
-CG_HD uint32_t scale_by_cdf(uint32_t spanm1, uint32_t c16) {
-    const uint64_t t = static_cast<uint64_t>(spanm1) * c16 + c16;
-    return static_cast<uint32_t>(t >> 32);
-}
-
 // Count of equal-top-bit shifts for the interval [low, high] (the |1 keeps it below 32 on a
 // degenerate interval, which only a corrupt table can produce).
 CG_HD int equal_shifts(uint32_t low, uint32_t high) { return cg_clz((low ^ high) | 1u); }
-// Count of underflow shifts once the top bits differ: the run, from bit 30 down, of positions where
-// low has a 1 and high a 0.
-CG_HD int underflow_shifts(uint32_t low, uint32_t high) { return cg_clz((((~low) | high) << 1) | 1u); }
-
 // ---- shared-memory access --------------------------------------------------------------------------------
 // A stream's table is the column tab[m][tid] = cdf[m] << 16 of a [rows][128] uint32 array, addressed
 // by byte address: entry m of the column starting at `col` is at col + m * kTableRowBytes.  The
@@ -323,12 +312,15 @@ CG_HD void decode_stream(Smem sm, uint32_t col, int maxsym, const uint8_t *strea
 }
 
 // ---- MSB-first bit writer into one scratch row (add_bits_to_output, enc_new.cu:21-97) ---------------------
+// Output bits collect in a 64-bit accumulator.  Whole 32-bit words leave it, big-endian, into the
+// stream's scratch row; the common case does that for the whole warp at once (see EncoderState::step)
+// so that the store is not a per-lane branch.
 struct BitSink {
     uint32_t *row;    // 4-byte aligned scratch row of this stream
     uint32_t cap_w;   // words that fit in the row
     uint32_t nwords;  // words produced so far (may exceed cap_w: then nothing more is stored)
     uint64_t acc;     // pending output bits, right-aligned
-    int nacc;         // number of bits in acc, < 32 between calls
+    uint32_t nacc;    // number of bits in acc, < 64
 
     CG_HD void init(uint8_t *p, int64_t stride) {
         row = reinterpret_cast<uint32_t *>(p);
@@ -337,31 +329,37 @@ struct BitSink {
         acc = 0;
         nacc = 0;
     }
-    // appends the low n (0..32) bits of v (v has no bits above n)
-    CG_HD void put(uint32_t v, int n) {
+    // appends the low n bits of v (v has no bits above n); needs nacc + n <= 64
+    CG_HD void put(uint32_t v, uint32_t n) {
         acc = (acc << n) | v;
         nacc += n;
-        if (nacc >= 32) {
-            nacc -= 32;
-            const uint32_t w = static_cast<uint32_t>(acc >> nacc);
-            if (nwords < cap_w) row[nwords] = cg_bswap32(w);
-            nwords++;
-        }
     }
-    // `count` copies of `bit`
+    // moves the oldest 32 bits out; needs nacc >= 32
+    CG_HD void store_word() {
+        nacc -= 32u;
+        const uint32_t w = static_cast<uint32_t>(acc >> nacc);
+        if (nwords < cap_w) row[nwords] = cg_bswap32(w);
+        nwords++;
+    }
+    CG_HD void drain() {
+        while (nacc >= 32u) store_word();
+    }
+    // `count` copies of `bit`, any count
     CG_HD void put_run(uint32_t bit, uint32_t count) {
         const uint32_t ones = 0u - bit;  // 0 or 0xFFFFFFFF
-        while (count >= 32u) {
-            put(ones, 32);
-            count -= 32u;
+        while (count) {
+            drain();
+            const uint32_t n = count < 32u ? count : 32u;
+            put(ones >> (32u - n), n);
+            count -= n;
         }
-        if (count) put(ones >> (32u - count), static_cast<int>(count));
     }
     // zero-fills to a byte boundary; returns the stream length in bytes
     CG_HD uint32_t finish() {
-        const uint32_t bytes = nwords * 4u + static_cast<uint32_t>((nacc + 7) >> 3);
+        drain();
+        const uint32_t bytes = nwords * 4u + ((nacc + 7u) >> 3);
         if (nacc) {
-            const uint32_t w = static_cast<uint32_t>(acc << (32 - nacc));
+            const uint32_t w = static_cast<uint32_t>(acc << (32u - nacc));
             if (nwords < cap_w) row[nwords] = cg_bswap32(w);
         }
         return bytes;
@@ -369,49 +367,64 @@ struct BitSink {
 };
 
 // ---- encoder state and step -----------------------------------------------------------------------------
+constexpr uint32_t kSinkHighWater = 48;  // a symbol starts with fewer bits than this in the accumulator
+constexpr uint32_t kFastEmitBits = 16;   // ... so up to this many more fit without a store
+
 struct EncoderState {
-    uint32_t low, high, pending;
+    uint32_t low, span32, pending;  // span32 = (high - low + 1) mod 2^32, 0 for the full range
     CG_HD void init() {
         low = 0u;
-        high = 0xFFFFFFFFu;
+        span32 = 0u;
         pending = 0u;
     }
-    // one symbol s in [0, maxsym] (enc_new.cu:257-295)
-    CG_HD void step(Smem sm, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out) {
+    // one symbol s in [0, maxsym] (enc_new.cu:257-295); the table column must have a readable row
+    // after the last symbol's.  lanes: the warp's lanes that encode together (same token count).
+    CG_HD void step(Smem sm, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out, uint32_t lanes) {
         const uint32_t a = col + s * kTableRowBytes;
-        const uint32_t spanm1 = high - low;
-        const uint32_t flo = scale_by_cdf(spanm1, sm.ld(a));
-        const uint32_t fhi = (s == maxsym) ? spanm1 + 1u : scale_by_cdf(spanm1, sm.ld(a + kTableRowBytes));
-        high = low + fhi - 1u;
-        low = low + flo;
+        const uint32_t flo = scale_exact(span32, sm.ld(a));
+        const uint32_t fnext = scale_exact(span32, sm.ld(a + kTableRowBytes));
+        const uint32_t fhi = (s == maxsym) ? span32 : fnext;
+        low += flo;
+        span32 = fhi - flo;
+        const uint32_t high = low + span32 - 1u;
         // equal-top-bit shifts: their n1 bits are low's top bits; the first is followed by the pending
         // (inverted) bits of earlier underflow shifts (enc_new.cu:275-287)
-        const int n1 = equal_shifts(low, high);
+        const uint32_t n1 = static_cast<uint32_t>(equal_shifts(low, high));
         if (n1) {
-            const uint32_t bits = low >> (32 - n1);
-            if (pending == 0u) {
-                out.put(bits, n1);
+            const uint32_t bits = low >> (32u - n1);
+            const uint32_t first = bits >> (n1 - 1u);
+            const uint32_t rest = bits & ((1u << (n1 - 1u)) - 1u);
+            const uint32_t total = n1 + pending;
+            if (total <= kFastEmitBits) {
+                const uint32_t run = ((1u << pending) - 1u) & (first - 1u);  // pending ones after a 0, zeros after a 1
+                out.put((first << (total - 1u)) | (run << (n1 - 1u)) | rest, total);
             } else {
-                const uint32_t first = bits >> (n1 - 1);
-                out.put(first, 1);
+                out.drain();
+                out.put(first, 1u);
                 out.put_run(1u - first, pending);
-                out.put(bits & ((1u << (n1 - 1)) - 1u), n1 - 1);
-                pending = 0u;
+                out.drain();
+                out.put(rest, n1 - 1u);
             }
-            low <<= n1;
-            high = cg_fshl(0xFFFFFFFFu, high, static_cast<uint32_t>(n1));
+            pending = 0u;
         }
-        // underflow shifts (enc_new.cu:288-293)
-        const int k = underflow_shifts(low, high);
-        pending += static_cast<uint32_t>(k);
-        low = (low << k) & 0x7FFFFFFFu;
-        high = cg_fshl(0xFFFFFFFFu, high, static_cast<uint32_t>(k)) | 0x80000000u;
+        // underflow shifts (enc_new.cu:288-293) only raise the pending count; both kinds of shift
+        // double the span
+        const uint32_t k = static_cast<uint32_t>(cg_clz(((((~low) | high) << n1) << 1) | 1u));
+        pending += k;
+        const uint32_t sh = (n1 + k) & 31u;
+        low = (low << sh) & 0x7FFFFFFFu;
+        span32 <<= sh;
+        // a store for every lane that has a full word, as soon as one lane is near the high-water mark
+        if (cg_any_lane(lanes, out.nacc >= kSinkHighWater)) {
+            if (out.nacc >= 32u) out.store_word();
+        }
     }
     // final flush (enc_new.cu:298-306); returns the stream length in bytes
     CG_HD uint32_t flush(BitSink &out) {
         pending += 1u;
         const uint32_t last = (low < 0x40000000u) ? 0u : 1u;
-        out.put(last, 1);
+        out.drain();
+        out.put(last, 1u);
         out.put_run(1u - last, pending);
         return out.finish();
     }

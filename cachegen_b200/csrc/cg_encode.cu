@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
     const int n = min(kSubTokens, p.ntokens - t0);
     const int maxsym = p.lp - 2;
 
-    stage_table_column(tab, p.cdf + g * p.lp, p.lp, p.lp - 1, tid);
+    stage_table_column(tab, p.cdf + g * p.lp, p.lp, p.lp, tid);
     const uint32_t col = smem_addr(tab + tid);
     const int64_t slot = static_cast<int64_t>(sub) * nrows * p.nchannels + g;
     BitSink out;
@@ -40,19 +40,23 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
     const int8_t *sp = p.sym + row * p.s0 + static_cast<int64_t>(t0) * p.s1 + c * p.s2;
     EncoderState enc;
     enc.init();
+    const uint32_t lanes = __activemask();
     bool bad_symbol = false;
 
+    const int64_t s1 = p.s1;
     for (int base = 0; base < n; base += kPrefetch) {
         uint32_t buf[kPrefetch];
 #pragma unroll
-        for (int j = 0; j < kPrefetch; ++j)
-            buf[j] = (base + j < n) ? static_cast<uint8_t>(__ldg(sp + static_cast<int64_t>(base + j) * p.s1)) : 0u;
+        for (int j = 0; j < kPrefetch; ++j) {
+            buf[j] = (base + j < n) ? static_cast<uint8_t>(__ldg(sp)) : 0u;
+            sp += s1;
+        }
 #pragma unroll
         for (int j = 0; j < kPrefetch; ++j) {
             if (base + j >= n) break;
             uint32_t s = buf[j];
             if (s > static_cast<uint32_t>(maxsym)) { s = maxsym; bad_symbol = true; }
-            enc.step(Smem{}, col, s, static_cast<uint32_t>(maxsym), out);
+            enc.step(Smem{}, col, s, static_cast<uint32_t>(maxsym), out, lanes);
         }
     }
     const uint32_t nbytes = enc.flush(out);
@@ -188,7 +192,7 @@ using namespace cg;
 
 static int launch_encode(const EncodeParams &p, int nrows, int nsub, cudaStream_t st) {
     const dim3 grid((p.nchannels + kGroup - 1) / kGroup, nrows, nsub), block(kGroup);
-    encode_kernel<<<grid, block, static_cast<size_t>(p.lp - 1) * kRowBytes, st>>>(p);
+    encode_kernel<<<grid, block, static_cast<size_t>(p.lp) * kRowBytes, st>>>(p);
     return check_launch();
 }
 

@@ -24,14 +24,14 @@ static std::vector<uint32_t> make_table(const uint16_t *cdf, int lp, int rows, i
 
 extern "C" int64_t hm_encode_stream(const uint16_t *cdf, int lp, const int8_t *sym, int n, uint8_t *out,
                                     int64_t cap, int tid) {
-    std::vector<uint32_t> tab = make_table(cdf, lp - 1, lp - 1, tid);
+    std::vector<uint32_t> tab = make_table(cdf, lp, lp, tid);
     Smem rd{reinterpret_cast<uint8_t *>(tab.data())};
     const uint32_t col = static_cast<uint32_t>(tid) * 4u;
     BitSink sink;
     sink.init(out, cap);
     EncoderState enc;
     enc.init();
-    for (int i = 0; i < n; ++i) enc.step(rd, col, static_cast<uint8_t>(sym[i]), static_cast<uint32_t>(lp - 2), sink);
+    for (int i = 0; i < n; ++i) enc.step(rd, col, static_cast<uint8_t>(sym[i]), static_cast<uint32_t>(lp - 2), sink, 0xFFFFFFFFu);
     return enc.flush(sink);
 }
 
