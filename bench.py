@@ -48,6 +48,9 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama7b-8k")
     ap.add_argument("--tokens", type=int, default=0, help="override the workload's token count")
+    ap.add_argument("--shard", default="requests", choices=["requests", "layers"],
+                    help="N > 1: one request per GPU (weak scaling, default) or the layers of ONE request "
+                         "split across the GPUs and the decoded KV gathered to GPU 0 over NCCL (strong scaling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the baseline sample")
@@ -242,7 +245,8 @@ def run_ours(args, spec):
     from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
     from cachegen_b200.serde import CacheGenDeserializer, CacheGenSerializer
     from cachegen_b200.serde.cachegen_basics import CacheGenGPUBytestream, CacheGenGPUEncoderOutput
-    from cachegen_b200.parallel import max_over_ranks
+    from cachegen_b200.parallel import gather_layers, max_over_ranks, partition
+    from cachegen_b200.serde.cachegen_basics import CacheGenConfig
     from cachegen_b200.synth import generate_kv
 
     rank = int(os.environ.get("RANK", "0"))
@@ -256,15 +260,24 @@ def run_ours(args, spec):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    L, H, D, T = spec["num_layers"], spec["num_heads"], spec["head_size"], spec["num_tokens"]
+    L_total, H, D, T = spec["num_layers"], spec["num_heads"], spec["head_size"], spec["num_tokens"]
     C = H * D
     config = LMCacheEngineConfig.from_defaults(chunk_size=CHUNK_TOKENS)
     meta = LMCacheEngineMetadata(model_name=spec["model_name"], world_size=world, worker_id=rank, fmt="vllm")
-    ser = CacheGenSerializer(config, meta)
-    de = CacheGenDeserializer(config, meta, out_dtype=torch.float16)
+    by_layers = args.shard == "layers" and world > 1
+    full_cfg = CacheGenConfig.from_model_name(spec["model_name"])
+    if by_layers:
+        mine = partition(L_total, world, rank)
+        if len(mine) == 0:
+            raise SystemExit("more GPUs than layers")
+        cfg, L, first_layer, seed = full_cfg.layer_slice(mine.start, mine.stop), len(mine), mine.start, spec["seed"]
+    else:
+        cfg, L, first_layer, seed = full_cfg, L_total, 0, spec["seed"] + 1000 * rank
+    ser = CacheGenSerializer(config, meta, cachegen_config=cfg)
+    de = CacheGenDeserializer(config, meta, cachegen_config=cfg, out_dtype=torch.float16)
 
-    # ---- set-up (untimed): this rank's request, encoded chunk by chunk as LMCacheEngine.store would
-    kv = generate_kv(L, H, D, T, spec["seed"] + 1000 * rank, key_rho=spec["key_rho"], device=dev, dtype=torch.float16)
+    # ---- set-up (untimed): this rank's share, encoded chunk by chunk as LMCacheEngine.store would
+    kv = generate_kv(L, H, D, T, seed, key_rho=spec["key_rho"], device=dev, dtype=torch.float16, first_layer=first_layer)
     ms_encode = None
     for attempt in range(2):  # the first pass warms the allocator (every chunk's outputs stay alive), the second is timed
         chunks = []
@@ -318,7 +331,17 @@ def run_ours(args, spec):
         sampler.start()
         time.sleep(0.3)
     # ---- the headline: full decode, inputs resident in HBM
-    ms_step = timed(plan.run, args.steps, max(3, args.warmup))
+    full_out = None
+    if by_layers:
+        if rank == 0:
+            full_out = torch.empty((L_total, 2, T, H, D), dtype=torch.float16, device=dev)
+
+        def step():
+            plan.run()
+            gather_layers(out, L_total, root=0, out=full_out)
+    else:
+        step = plan.run
+    ms_step = timed(step, args.steps, max(3, args.warmup))
     # ---- the dominant kernel alone (offsets already in place)
     ms_kernel = timed(plan.run_decode, args.steps, 1)
     ms_offsets = timed(plan.run_offsets, args.steps, 1)
@@ -327,7 +350,7 @@ def run_ours(args, spec):
 
     # ---- end to end: encoded chunks in pinned host memory, copied in every step
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and not by_layers:
         def pin(t):
             return t.detach().cpu().pin_memory()
         host_chunks = [CacheGenGPUEncoderOutput(
@@ -359,12 +382,15 @@ def run_ours(args, spec):
 
     peak, peak_kind = measured_hbm_peak()
     achieved = algorithmic / ms_kernel / 1e6
+    total_kv_bytes = 2 * L_total * C * T * 2 if by_layers else world * kv_bytes
     line = {
-        "metric": "decoded_kv_gbps", "value": world * kv_bytes / ms_step / 1e6, "unit": "GB/s",
+        "metric": "decoded_kv_gbps", "value": total_kv_bytes / ms_step / 1e6, "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
-        "config": describe(spec, args),
-        "tokens_per_s": world * T / ms_step * 1e3,
+        "higher_is_better": True, "scaling": "strong" if by_layers else "weak", "vs_baseline": None, "dtype": "u32",
+        "data": "synthetic", "config": dict(describe(spec, args), shard=args.shard if world > 1 else "none",
+                                             delivery="NCCL send/recv of each rank's layer slab to GPU 0, inside the step"
+                                             if by_layers else "none"),
+        "tokens_per_s": (T if by_layers else world * T) / ms_step * 1e3,
         "bytes_per_token": per_token,
         "kv_bytes_per_token": kv_bytes / T,
         "gpu_launches": plan.launches * args.steps,

@@ -238,9 +238,12 @@ struct DecoderState {
         const uint32_t high = low + span32 - 1u;
         const uint32_t n1 = static_cast<uint32_t>(equal_shifts(low, high));
         const uint32_t k = static_cast<uint32_t>(cg_clz(((((~low) | high) << n1) << 1) | 1u));
-        const uint32_t s = (n1 + k) & 31u;  // at most 18 for any strictly increasing table
-        low = (low << s) & 0x7FFFFFFFu;
-        span32 <<= s;
+        const uint32_t s = n1 + k;  // at most 18 for any strictly increasing table; shifts below wrap at 32
+        // The reference also clears low's top bit after underflow shifts.  Here low is only ever
+        // compared with high = low + span - 1 bit by bit, offset carries value - low separately, and
+        // a set top bit flips the top bit of low and high alike: it changes neither shift count.
+        low = cg_fshl(0u, low, s);
+        span32 = cg_fshl(0u, span32, s);
         offset = cg_fshl(bw.hi, offset, s);
         bw.consume(s);
     }

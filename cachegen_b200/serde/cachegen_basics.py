@@ -52,6 +52,15 @@ class CacheGenConfig:
                        key_third_bins=d(self.key_third_bins), value_first_bins=d(self.value_first_bins),
                        value_second_bins=d(self.value_second_bins))
 
+    def layer_slice(self, start: int, stop: int) -> "CacheGenConfig":
+        """The settings of layers [start, stop) as a configuration of their own (layer-sharded runs)."""
+        n = stop - start
+        if not 0 <= start < stop <= self.key_third_layers:
+            raise ValueError(f"bad layer range [{start}, {stop}) of {self.key_third_layers}")
+        clip = lambda b: min(max(b - start, 0), n)
+        return replace(self, key_first_layers=clip(self.key_first_layers), key_second_layers=clip(self.key_second_layers),
+                       key_third_layers=n, value_first_layers=clip(self.value_first_layers))
+
     @staticmethod
     def from_model_name(model_name: str) -> "CacheGenConfig":
         """Same lookup as cachegen_basics.py:23-96: any name containing "Mistral-7B" reads the

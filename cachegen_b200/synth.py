@@ -54,14 +54,15 @@ def _slab(seed: int, layer: int, which: int, T: int, C: int, rho: float, sigma: 
 
 def generate_kv(num_layers: int, num_heads: int, head_size: int, num_tokens: int, seed: int,
                 key_rho: float = 0.9, value_rho: float = 0.6, device="cpu", dtype=torch.float16,
-                out_device=None) -> torch.Tensor:
-    """Returns a "vllm"-format blob [L, 2, T, H, D] in `dtype` on `out_device` (default: `device`)."""
+                out_device=None, first_layer: int = 0) -> torch.Tensor:
+    """Returns a "vllm"-format blob [L, 2, T, H, D] in `dtype` on `out_device` (default: `device`):
+    layers first_layer .. first_layer + num_layers - 1 of the cache with this seed."""
     C = num_heads * head_size
     out_device = out_device or device
     out = torch.empty((num_layers, 2, num_tokens, num_heads, head_size), dtype=dtype, device=out_device)
     for l in range(num_layers):
-        k = _slab(seed, l, 0, num_tokens, C, key_rho, 0.5, 0.02, device)
-        v = _slab(seed, l, 1, num_tokens, C, value_rho, 0.3, 0.0, device)
+        k = _slab(seed, first_layer + l, 0, num_tokens, C, key_rho, 0.5, 0.02, device)
+        v = _slab(seed, first_layer + l, 1, num_tokens, C, value_rho, 0.3, 0.0, device)
         out[l, 0] = k.view(num_tokens, num_heads, head_size).to(dtype).to(out_device)
         out[l, 1] = v.view(num_tokens, num_heads, head_size).to(dtype).to(out_device)
     return out
