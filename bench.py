@@ -8,9 +8,10 @@ seed 1, 7B-default bins, one serializer call per 256 tokens -- synthetic AR(1) K
 standing in for real model KV.
 
   value        whole-job decoded-KV throughput with the encoded chunks resident in HBM (CUDA events)
-  e2e          the same through CacheGenDeserializer.decode_many with the encoded chunks in pinned host
-               memory: host->device copies of every step's inputs and a device->host read of the status
-               word inside the timed region
+  e2e          the same through CacheGenDeserializer.decode_many_host with the encoded chunks (CGB2
+               containers) in pinned host memory: host->device copies of every step's inputs and a
+               device->host read of the status word inside the timed region; e2e_reference_blob_tensors is
+               the same call on the tensors of the reference's own blob layout
   roofline     the dominant kernel (fused decode + dequantise + KV store) timed alone, algorithmic bytes
                over its duration against the measured HBM copy bandwidth
   cpu_baseline the CPU oracle's decode + dequantise on a bounded sample of the same chunks, all host cores
@@ -307,7 +308,7 @@ def run_ours(args, spec):
     ref = kv[:, :, :CHUNK_TOKENS].reshape(L, 2, -1, C).transpose(0, 1).reshape(2 * L, -1, C).float()
     bound = 0.5 * step / cq[:, None, None] * 1.001 + step * 2.0 ** -10 + 1e-6
     assert bool(((got - ref).abs() <= bound).all()), "decoded KV violates the quantiser's error bound"
-    del got, ref, kv
+    del got, ref
 
     def barrier():
         if world > 1:
@@ -350,30 +351,49 @@ def run_ours(args, spec):
 
     # ---- end to end: encoded chunks in pinned host memory, copied in every step
     e2e = None
+    extra = {}
     if not args.no_e2e and not by_layers:
         def pin(t):
             return t.detach().cpu().pin_memory()
+        status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+
+        def measure_host(host_chunks, nbytes, what):
+            def e2e_step():
+                de.decode_many_host(host_chunks, out=out, groups=8)
+                status_host.copy_(de.group_status_words()[-1], non_blocking=True)
+            ms = timed(e2e_step, max(2, args.steps // 2), 2)
+            torch.cuda.synchronize()
+            assert int(status_host.item()) == 0
+            de.check_status()
+            return {"value": world * kv_bytes / ms / 1e6, "unit": "GB/s", "h2d_bytes_per_step": nbytes,
+                    "d2h_bytes_per_step": 4, "ms_per_step": ms, "tokens_per_s": world * T / ms * 1e3, "api": what}
+
+        # (1) the library's own container (CGB2: one buffer per chunk, tables as byte counts)
+        flat_gpu = [ser.encode_flat(kv[:, :, s:s + CHUNK_TOKENS]) for s in range(0, T, CHUNK_TOKENS)]
+        flat_plan = de.plan(flat_gpu, out=out)
+        ms_flat = timed(flat_plan.run, args.steps, 2)
+        extra["value_flat_container"] = {"value": world * kv_bytes / ms_flat / 1e6, "unit": "GB/s", "ms_per_step": ms_flat,
+                                         "what": "as `value`, chunks held as CGB2 containers in HBM"}
+        extra["bytes_per_token_flat_container"] = {
+            "payload": flat_plan.payload_bytes / T, "tables": flat_plan.table_bytes / T,
+            "lengths": flat_plan.length_bytes / T, "scales": flat_plan.scale_bytes / T,
+            "container": sum(c.header.total for c in flat_gpu) / T}
+        flat_host = [c.pin_memory() for c in flat_gpu]
+        del flat_plan, flat_gpu, kv
+        e2e = measure_host(flat_host, sum(c.header.total for c in flat_host),
+                           "CacheGenDeserializer.decode_many_host on CGB2 containers (CacheGenSerializer.encode_flat) "
+                           "held in pinned host memory; 8 groups, copies of one group overlap the decode of the previous")
+        del flat_host
+        # (2) the reference's blob layout (tensors of CacheGenGPUEncoderOutput), same call
         host_chunks = [CacheGenGPUEncoderOutput(
             [CacheGenGPUBytestream(pin(dc.bytestream), pin(dc.bytestream_lengths), dc.ntokens) for dc in eo.data_chunks],
             pin(eo.cdf), pin(eo.max_tensors_key), pin(eo.max_tensors_value), eo.num_heads, eo.head_size) for eo in chunks]
         h2d = sum(t.numel() * t.element_size() for eo in host_chunks
                   for t in [eo.cdf, eo.max_tensors_key, eo.max_tensors_value] +
                   [x for dc in eo.data_chunks for x in (dc.bytestream, dc.bytestream_lengths)])
-        status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
-
-        def e2e_step():
-            de.decode_many_host(host_chunks, out=out, groups=4)
-            words = de.group_status_words()
-            status_host.copy_(words[-1], non_blocking=True)
-
-        ms_e2e = timed(e2e_step, max(2, args.steps // 2), 2)
-        torch.cuda.synchronize()
-        assert int(status_host.item()) == 0
-        de.check_status()
-        e2e = {"value": world * kv_bytes / ms_e2e / 1e6, "unit": "GB/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e, "tokens_per_s": world * T / ms_e2e * 1e3,
-               "api": "CacheGenDeserializer.decode_many_host on encoded chunks held in pinned host memory "
-                      "(4 groups, copies of one group overlap the decode of the previous one)"}
+        extra["e2e_reference_blob_tensors"] = measure_host(
+            host_chunks, h2d, "the same call on the tensors of the reference's blob (int16 tables, int32 lengths) in pinned host memory")
+        del host_chunks
 
     if rank != 0:
         if world > 1:
@@ -409,6 +429,7 @@ def run_ours(args, spec):
     }
     if e2e:
         line["e2e"] = e2e
+    line.update(extra)
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = run_cpu_baseline(spec, args.cpu_seconds)
     print(json.dumps(line), flush=True)

@@ -10,8 +10,10 @@ CG_F16, CG_BF16 = 0, 1
 CG_MAX_TOKENS_PER_STREAM = 256
 CG_MAX_LP = 64
 CG_GROUP_CHANNELS = 128
-CG_MAX_DECODE_JOBS = 48
-CG_S_STREAM_OVERFLOW, CG_S_BAD_LENGTHS, CG_S_BAD_SYMBOL = 1, 2, 4
+CG_MAX_DECODE_JOBS = 40
+CG_S_STREAM_OVERFLOW, CG_S_BAD_LENGTHS, CG_S_BAD_SYMBOL, CG_S_COUNT_OVERFLOW = 1, 2, 4, 8
+CG_TABLES_CDF, CG_TABLES_COUNTS = 0, 1
+CG_LENGTHS_I32, CG_LENGTHS_U16 = 0, 1
 CG_E_CUDA = -8
 
 
@@ -22,16 +24,19 @@ def stream_capacity(ntokens):
 class DecodeJob(ctypes.Structure):
     """cg_decode_job"""
     _fields_ = [
-        ("cdf", ctypes.c_void_p),
+        ("tables", ctypes.c_void_p),
         ("bytes", ctypes.c_void_p),
         ("lengths", ctypes.c_void_p),
         ("group_off", ctypes.c_void_p),
         ("scales_k", ctypes.c_void_p),
         ("scales_v", ctypes.c_void_p),
         ("out", ctypes.c_void_p),
+        ("table_row_off", ctypes.c_void_p),
         ("nbytes", ctypes.c_int64),
         ("ntokens", ctypes.c_int32),
         ("scale_stride", ctypes.c_int32),
+        ("table_kind", ctypes.c_int32),
+        ("length_kind", ctypes.c_int32),
     ]
 
 
@@ -70,7 +75,7 @@ def lib():
     L.cg_encode_padded.argtypes = [p, p, S3, i, i, i, i, p, i64, p, p, p]
     L.cg_decode_padded.argtypes = [p, p, i64, p, p, S3, i, i, i, i, p, p]
     L.cg_decode_prefsum.argtypes = [p, p, i64, p, p, S3, i, i, i, i, p, p]
-    L.cg_quantize_cdf.argtypes = [p, i, i64, i64, i64, i64, i, i, i, i, p, i, p, p, p, p]
+    L.cg_quantize_cdf.argtypes = [p, i, i64, i64, i64, i64, i, i, i, i, p, i, p, p, p, p, p, p, p]
     L.cg_encode_chunk.argtypes = [p, p, i, i, i, i, p, i64, p, p, p, p, p]
     L.cg_compact_streams.argtypes = [p, i64, p, p, p, i, i, i, p, p]
     L.cg_decode_offsets.argtypes = [ctypes.POINTER(DecodeJob), i, i, i, p, p, p]
@@ -108,4 +113,6 @@ def status_text(bits):
         names.append("stream lengths are negative or do not match the byte array")
     if bits & CG_S_BAD_SYMBOL:
         names.append("a symbol outside the table was met while encoding")
+    if bits & CG_S_COUNT_OVERFLOW:
+        names.append("a histogram count does not fit the byte-count tables")
     return "; ".join(names) if names else "ok"

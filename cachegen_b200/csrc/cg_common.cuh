@@ -53,6 +53,35 @@ __device__ __forceinline__ void stage_table_column(uint32_t *tab, const int16_t 
     for (int m = n; m < rows; ++m) tab[m * kGroup + tid] = 0u;
 }
 
+// The same column from the byte counts of the non-centre symbols (CG_TABLES_COUNTS):
+// cdf[i] = (uint16)((0xFFFF - max_bins) * #{sym < i} / ntokens) + i, as calculate_cdf builds it
+// (cal_cdf.cu:11-15,40-49 in the reference).  cnt points at this channel's first count; counts of one
+// symbol are `stride` bytes apart; cq = bins // 2 - 1 is the centre symbol, whose count is implied.
+__device__ __forceinline__ void stage_table_column_from_counts(uint32_t *tab, const uint8_t *cnt, int64_t stride,
+                                                               int cq, int ntokens, int lp, int rows, int tid) {
+    const int max_bins = lp - 1;
+    uint32_t others = 0;
+    for (int j = 0; j < 2 * cq; ++j) others += __ldg(cnt + j * stride);
+    const uint32_t centre = static_cast<uint32_t>(ntokens) - others;
+    const uint32_t scale = 0xFFFFu - static_cast<uint32_t>(max_bins);
+    const uint32_t total = static_cast<uint32_t>(ntokens) & 0xFFFFu;
+    const bool pow2 = (total & (total - 1u)) == 0u;
+    const int sh = 31 - __clz(static_cast<int>(total | 1u));
+    const int n = lp < rows ? lp : rows;
+    uint32_t cum = 0;
+    for (int i = 0; i < n; ++i) {
+        const uint32_t prod = scale * (cum & 0xFFFFu);
+        const uint32_t nv = total ? (pow2 ? (prod >> sh) : (prod / total)) : 0u;
+        tab[i * kGroup + tid] = ((nv + static_cast<uint32_t>(i)) & 0xFFFFu) << 16;
+        uint32_t count = 0;
+        if (i < cq) count = __ldg(cnt + i * stride);
+        else if (i == cq) count = centre;
+        else if (i <= 2 * cq) count = __ldg(cnt + (i - 1) * stride);
+        cum += count;
+    }
+    for (int i = n; i < rows; ++i) tab[i * kGroup + tid] = 0u;
+}
+
 // ---- block-wide exclusive scan over kGroup (=128) ints ------------------------------------------
 // warp_sums: shared int[4].  Returns the exclusive prefix of `v` across the block.
 __device__ __forceinline__ int block_exclusive_scan_128(int v, int *warp_sums, int tid, int *total) {

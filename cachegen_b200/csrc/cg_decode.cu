@@ -90,7 +90,10 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
     const int64_t g = static_cast<int64_t>(row) * p.nchannels + c;
 
     // stream offsets: group base + exclusive scan of this block's lengths (cachegen_decoder.py:70)
-    int len = active ? __ldg(job.lengths + g) : 0;
+    int len = 0;
+    if (active)
+        len = job.length_kind == CG_LENGTHS_U16 ? static_cast<int>(__ldg(static_cast<const uint16_t *>(job.lengths) + g))
+                                                : __ldg(static_cast<const int32_t *>(job.lengths) + g);
     bool bad = false;
     if (len < 0) { len = 0; bad = true; }
     if (len > (1 << 20)) { len = 1 << 20; bad = true; }
@@ -109,7 +112,15 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
         lut[tid] = __fdiv_rn(__fsub_rn(static_cast<float>(tid), cq), cq);
     }
     const int rows = table_rows(p.lp, LEVELS);
-    if (active) stage_table_column(smem, job.cdf + g * p.lp, p.lp, rows, tid);
+    if (active) {
+        if (job.table_kind == CG_TABLES_COUNTS) {
+            const int cq = static_cast<int>(half_range(__ldg(p.bins + row)));
+            const uint8_t *cnt = static_cast<const uint8_t *>(job.tables) + __ldg(job.table_row_off + row) + c;
+            stage_table_column_from_counts(smem, cnt, p.nchannels, cq, job.scale_stride, p.lp, rows + 1, tid);
+        } else {
+            stage_table_column(smem, static_cast<const int16_t *>(job.tables) + g * p.lp, p.lp, rows + 1, tid);
+        }
+    }
     __syncthreads();
     if (!active) return;
 
@@ -256,9 +267,12 @@ extern "C" int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int 
     p.status = status;
     for (int j = 0; j < njobs; ++j) {
         const cg_decode_job &jb = jobs_host[j];
-        if (!jb.cdf || !jb.lengths || !jb.group_off || !jb.scales_k || !jb.scales_v || !jb.out ||
-            (!jb.bytes && jb.nbytes > 0))
+        if (!jb.tables || !jb.lengths || !jb.group_off || !jb.scales_k || !jb.scales_v || !jb.out ||
+            (!jb.bytes && jb.nbytes > 0) || (jb.table_kind == CG_TABLES_COUNTS && !jb.table_row_off))
             return CG_E_NULL;
+        if ((jb.table_kind != CG_TABLES_CDF && jb.table_kind != CG_TABLES_COUNTS) ||
+            (jb.length_kind != CG_LENGTHS_I32 && jb.length_kind != CG_LENGTHS_U16))
+            return CG_E_SHAPE;
         if (jb.ntokens <= 0 || jb.nbytes < 0) return CG_E_SHAPE;
         if (jb.ntokens > CG_MAX_TOKENS_PER_STREAM) return CG_E_TOKENS;
         p.jobs[j] = jb;

@@ -73,8 +73,9 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
 // Segments are either the sub-chunks of one encode call (flat lengths array [nseg, nrows*C]) or the
 // jobs of one decode call (one lengths pointer and one expected byte total per job).
 struct SegmentList {
-    const int32_t *lengths[CG_MAX_DECODE_JOBS];
+    const void *lengths[CG_MAX_DECODE_JOBS];
     int64_t expect[CG_MAX_DECODE_JOBS];
+    int32_t kind[CG_MAX_DECODE_JOBS];  // CG_LENGTHS_*
 };
 
 // Level 1: one warp per 128-channel group sums the group's lengths into sums[nseg, nrows*nslab].
@@ -88,13 +89,15 @@ __global__ void group_sums_kernel(const __grid_constant__ SegmentList segs, cons
     if (wid >= static_cast<int64_t>(nseg) * ngroups) return;
     const int seg = static_cast<int>(wid / ngroups), gid = static_cast<int>(wid % ngroups);
     const int row = gid / nslab, slab = gid % nslab;
-    const int32_t *len = BY_JOB ? segs.lengths[seg]
+    const bool u16 = BY_JOB && segs.kind[seg] == CG_LENGTHS_U16;
+    const int32_t *len = BY_JOB ? static_cast<const int32_t *>(segs.lengths[seg])
                                 : flat_lengths + static_cast<int64_t>(seg) * nrows * nchannels;
+    const uint16_t *len16 = reinterpret_cast<const uint16_t *>(len) + static_cast<int64_t>(row) * nchannels;
     len += static_cast<int64_t>(row) * nchannels;
     int64_t s = 0;
     bool bad = false;
     for (int c = slab * kGroup + lane; c < min(nchannels, (slab + 1) * kGroup); c += 32) {
-        int v = __ldg(len + c);
+        int v = u16 ? static_cast<int>(__ldg(len16 + c)) : __ldg(len + c);
         if (v < 0) { v = 0; bad = true; }
         if (v > (1 << 20)) { v = 1 << 20; bad = true; }
         s += v;
@@ -260,6 +263,7 @@ extern "C" int cg_decode_offsets(const cg_decode_job *jobs_host, int njobs, int 
         if (!jobs_host[j].lengths) return CG_E_NULL;
         segs.lengths[j] = jobs_host[j].lengths;
         segs.expect[j] = jobs_host[j].nbytes;
+        segs.kind[j] = jobs_host[j].length_kind;
     }
     const int nslab = (nchannels + kGroup - 1) / kGroup;
     const int ngroups = nrows * nslab;

@@ -94,7 +94,8 @@ template <int DT, int VEC>
 __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
     const uint16_t *__restrict__ kv, const KvLayout L, const float *__restrict__ bins,
     const uint16_t *__restrict__ scales, int max_bins, int8_t *__restrict__ sym_out,
-    int16_t *__restrict__ cdf_out) {
+    int16_t *__restrict__ cdf_out, uint8_t *__restrict__ counts_out, const int64_t *__restrict__ table_row_off,
+    int32_t *status) {
     extern __shared__ uint32_t hist[];  // [max_bins+1][kGroup], then uint16 tables [kGroup][lp]
     const int lp = max_bins + 1;
     uint16_t *out16 = reinterpret_cast<uint16_t *>(hist + lp * kGroup);
@@ -165,6 +166,27 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
     }
     __syncthreads();
     if (tid < kGroup && c0 + tid < C) counts_to_table(hist, max_bins, tid, out16);
+    if (counts_out) {
+        // byte counts of the non-centre symbols, [symbol][channel] so that a warp writes a run of bytes
+        const int cq = static_cast<int>(MAX);
+        uint8_t *dst = counts_out + __ldg(table_row_off + row) + c0;
+        bool overflow = false;
+        for (int i = tid; i < 2 * cq * kGroup; i += kQuantThreads) {
+            const int jj = i / kGroup, cl = i - jj * kGroup;
+            const int sym = jj < cq ? jj : jj + 1;
+            const uint32_t n = (sym < max_bins) ? hist[(sym + 1) * kGroup + cl] : 0u;
+            if (c0 + cl < C) {
+                dst[static_cast<int64_t>(jj) * C + cl] = static_cast<uint8_t>(n);
+                overflow |= n > 255u;
+            }
+        }
+        // a symbol above 2*Cq (which the quantiser never produces) has no place in the byte counts
+        for (int i = tid; i < (max_bins - 2 * cq - 1) * kGroup; i += kQuantThreads) {
+            const int sym = 2 * cq + 1 + i / kGroup, cl = i % kGroup;
+            overflow |= (c0 + cl < C) && hist[(sym + 1) * kGroup + cl] != 0u;
+        }
+        if (overflow && status) atomicOr(status, CG_S_COUNT_OVERFLOW);
+    }
     __syncthreads();
     store_tables(out16, cdf_out, row, c0, C, lp, tid, kQuantThreads);
 }
@@ -219,8 +241,10 @@ extern "C" int cg_calculate_cdf(const int8_t *sym, const int64_t sym_strides[3],
 extern "C" int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
                                int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
                                const float *bins, int max_bins, int8_t *sym_out, void *scales_out,
-                               int16_t *cdf_out, void *stream) {
+                               int16_t *cdf_out, uint8_t *counts_out, const int64_t *table_row_off,
+                               int32_t *status, void *stream) {
     if (!kv || !bins || !sym_out || !scales_out || !cdf_out) return CG_E_NULL;
+    if (counts_out && !table_row_off) return CG_E_NULL;
     if (nlayers <= 0 || ntokens <= 0 || nheads <= 0 || head_size <= 0 || 2 * nlayers > 65535) return CG_E_SHAPE;
     if (max_bins < 1 || max_bins >= CG_MAX_LP) return CG_E_LP;
     if (ntokens >= 65536) return CG_E_HIST;
@@ -242,7 +266,8 @@ extern "C" int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64
     const dim3 grid((C + kGroup - 1) / kGroup, nrows);
     const size_t smem = hist_smem_bytes(max_bins);
 #define CG_LAUNCH_Q(DT, V) \
-    quantize_cdf_kernel<DT, V><<<grid, kQuantThreads, smem, st>>>(x, L, bins, sc, max_bins, sym_out, cdf_out)
+    quantize_cdf_kernel<DT, V><<<grid, kQuantThreads, smem, st>>>(x, L, bins, sc, max_bins, sym_out, cdf_out, \
+                                                                  counts_out, table_row_off, status)
     if (dtype == CG_F16) { if (vec) CG_LAUNCH_Q(CG_F16, 8); else CG_LAUNCH_Q(CG_F16, 1); }
     else { if (vec) CG_LAUNCH_Q(CG_BF16, 8); else CG_LAUNCH_Q(CG_BF16, 1); }
 #undef CG_LAUNCH_Q

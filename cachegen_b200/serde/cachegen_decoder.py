@@ -15,6 +15,7 @@ from .. import _lib
 from .. import torchac_cuda
 from ..config import LMCacheEngineConfig, LMCacheEngineMetadata
 from . import cachegen_basics as CGBasics
+from . import flat_format
 from .cachegen_basics import CacheGenConfig, CacheGenGPUBytestream, CacheGenGPUEncoderOutput
 from .serde import Deserializer
 
@@ -59,6 +60,7 @@ def decode_function_gpu(cdf: torch.Tensor, data_chunks: List[CacheGenGPUBytestre
 
 
 def _check_chunk(eo: CacheGenGPUEncoderOutput):
+    """Shape checks of an unpickled reference blob -> (L, C, lp, T)."""
     cdf = eo.cdf
     if cdf.dim() != 3 or cdf.dtype != torch.int16:
         raise RuntimeError("CDF must be an int16 tensor [2L, C, Lp]")
@@ -82,11 +84,73 @@ def _to_device(t: torch.Tensor, dev) -> torch.Tensor:
     return t.to(dev, non_blocking=True)
 
 
+class _ChunkView:
+    """What a decode needs from one encoded chunk, whichever container it came in, on the GPU."""
+
+    def __init__(self, eo, dev, bins_cpu):
+        self.keep = []
+        if isinstance(eo, flat_format.FlatChunk):
+            fc = eo if eo.blob.device == dev else eo.to(dev, non_blocking=True)
+            h = fc.header
+            self.L, self.H, self.D, self.T, self.lp = h.L, h.H, h.D, h.T, h.lp
+            self.C = h.H * h.D
+            self.scale_dtype = fc.scale_dtype
+            sc = fc.scales()
+            self.mk, self.mv = sc[:h.L], sc[h.L:]
+            self.tables = fc.tables()
+            self.table_kind = h.table_kind
+            if h.table_kind == flat_format.TABLES_COUNTS:
+                need = flat_format.table_row_offsets(bins_cpu, self.C)[-1]
+                if h.off_lengths - h.off_tables < need:
+                    raise RuntimeError("the container's byte-count tables are smaller than the configured bins need")
+            self.length_kind = h.length_kind
+            self.subs = [(fc.payload(j), fc.lengths(j), fc.sub_tokens(j)) for j in range(h.nsub)]
+            self.table_bytes = h.off_lengths - h.off_tables
+            self.length_bytes = h.off_payload - h.off_lengths
+            self.keep.append(fc.blob)
+        else:
+            L, C, lp, T = _check_chunk(eo)
+            self.L, self.C, self.lp, self.T = L, C, lp, T
+            self.H, self.D = eo.num_heads, eo.head_size
+            self.scale_dtype = eo.max_tensors_key.dtype
+            self.mk = _to_device(eo.max_tensors_key, dev).reshape(L, T).contiguous()
+            self.mv = _to_device(eo.max_tensors_value, dev).reshape(L, T).contiguous()
+            self.tables = _to_device(eo.cdf, dev).contiguous()
+            self.table_kind = _lib.CG_TABLES_CDF
+            self.length_kind = _lib.CG_LENGTHS_I32
+            self.subs = []
+            for dc in eo.data_chunks:
+                if dc.bytestream.dtype != torch.uint8 or dc.bytestream.dim() != 1:
+                    raise RuntimeError("bytestream must be a 1-D uint8 tensor")
+                if dc.bytestream_lengths.dtype != torch.int32 or dc.bytestream_lengths.numel() != 2 * L * C:
+                    raise RuntimeError("bytestream_lengths must be int32 [2L, C]")
+                self.subs.append((_to_device(dc.bytestream, dev).contiguous(),
+                                  _to_device(dc.bytestream_lengths, dev).contiguous(), dc.ntokens))
+            self.table_bytes = self.tables.numel() * 2
+            self.length_bytes = len(self.subs) * 2 * L * C * 4
+            self.keep += [self.mk, self.mv, self.tables] + [t for s in self.subs for t in s[:2]]
+        if sum(s[2] for s in self.subs) != self.T:
+            raise RuntimeError("sub-chunk token counts do not add up to the chunk's tokens")
+        for _, _, ntok in self.subs:
+            if not 0 < ntok <= CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK:
+                raise RuntimeError("a sub-chunk holds 1..256 tokens")
+
+
+def _on_gpu(eo) -> bool:
+    return eo.blob.is_cuda if isinstance(eo, flat_format.FlatChunk) else eo.cdf.is_cuda
+
+
+def _device_of(eo):
+    return eo.blob.device if isinstance(eo, flat_format.FlatChunk) else eo.cdf.device
+
+
 class DecodePlan:
     """Everything cg_decode_offsets / cg_decode_dequant need for a list of encoded chunks, built once:
-    device-resident inputs, the job descriptors, the output blob and the launch arguments."""
+    device-resident inputs, the job descriptors, the output blob and the launch arguments.  Chunks are
+    CacheGenGPUEncoderOutput objects (the reference's blob, unpickled) or flat_format.FlatChunk
+    containers, on the GPU or in (pinned) host memory."""
 
-    def __init__(self, encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Tensor, fmt: str,
+    def __init__(self, encoder_outputs: list, bins: torch.Tensor, fmt: str,
                  out_dtype: torch.dtype, out: torch.Tensor = None, workspace: dict = None, device=None):
         if not encoder_outputs:
             raise RuntimeError("nothing to decode")
@@ -94,17 +158,23 @@ class DecodePlan:
             raise ValueError(f"unknown KV format {fmt!r}")
         first = encoder_outputs[0]
         dev = torch.device(device) if device is not None else (
-            first.cdf.device if first.cdf.is_cuda else torch.device("cuda", torch.cuda.current_device()))
-        NL, C, lp = first.cdf.shape
-        L = NL // 2
-        H, D = first.num_heads, first.head_size
-        scale_dtype = first.max_tensors_key.dtype
-        total_T = 0
-        for eo in encoder_outputs:
-            l2, c2, lp2, T = _check_chunk(eo)
-            if (l2, c2, lp2, eo.num_heads, eo.max_tensors_key.dtype) != (L, C, lp, H, scale_dtype):
+            _device_of(first) if _on_gpu(first) else torch.device("cuda", torch.cuda.current_device()))
+        ws = workspace if workspace is not None else {}
+        bins_cpu = ws.get("bins_cpu")
+        if bins_cpu is None or bins_cpu.numel() != bins.numel():
+            bins_cpu = bins.cpu()
+            ws["bins_cpu"] = bins_cpu
+        with torch.cuda.device(dev):
+            views = [_ChunkView(eo, dev, bins_cpu) for eo in encoder_outputs]
+        v0 = views[0]
+        L, C, lp, H, D, scale_dtype = v0.L, v0.C, v0.lp, v0.H, v0.D, v0.scale_dtype
+        NL = 2 * L
+        for v in views:
+            if (v.L, v.C, v.lp, v.H, v.scale_dtype) != (L, C, lp, H, scale_dtype):
                 raise RuntimeError("chunks of one decode call must share layers, channels, table length and dtype")
-            total_T += T
+        if scale_dtype not in _DTYPES:
+            raise TypeError(f"scales must be float16 or bfloat16, got {scale_dtype}")
+        total_T = sum(v.T for v in views)
         if bins.numel() != NL:
             raise RuntimeError(f"bins describe {bins.numel() // 2} layers, the blob has {L}")
         shape = (L, 2, total_T, H, D) if fmt == "vllm" else (L, 2, H, total_T, D)
@@ -118,8 +188,7 @@ class DecodePlan:
             o_layer, o_kv, o_head, o_token = out.stride(0), out.stride(1), out.stride(2), out.stride(3)
         nslab = (C + _lib.CG_GROUP_CHANNELS - 1) // _lib.CG_GROUP_CHANNELS
         ngroups = NL * nslab
-        njobs_total = sum(len(eo.data_chunks) for eo in encoder_outputs)
-        ws = workspace if workspace is not None else {}
+        njobs_total = sum(len(v.subs) for v in views)
         goff = ws.get("group_off")
         if goff is None or goff.numel() < njobs_total * ngroups or goff.device != dev:
             goff = torch.empty(njobs_total * ngroups, dtype=torch.int64, device=dev)
@@ -128,45 +197,42 @@ class DecodePlan:
         if status is None or status.device != dev:
             status = torch.zeros(1, dtype=torch.int32, device=dev)
             ws["status"] = status
+        row_off = None
+        if any(v.table_kind == _lib.CG_TABLES_COUNTS for v in views):
+            row_off = ws.get("table_row_off")
+            if row_off is None or row_off.device != dev or ws.get("table_row_off_c") != C:
+                row_off = torch.tensor(flat_format.table_row_offsets(bins_cpu, C), dtype=torch.int64, device=dev)
+                ws["table_row_off"], ws["table_row_off_c"] = row_off, C
 
         esz = out.element_size()
-        self.keep = []  # tensors that must outlive the launches
+        self.keep = [row_off] if row_off is not None else []  # tensors that must outlive the launches
         jobs_all = []
-        self.payload_bytes = 0
+        self.payload_bytes = self.table_bytes = self.length_bytes = 0
         t0 = 0
-        with torch.cuda.device(dev):
-            for eo in encoder_outputs:
-                T = eo.max_tensors_key.shape[1]
-                mk = _to_device(eo.max_tensors_key, dev).reshape(L, T).contiguous()
-                mv = _to_device(eo.max_tensors_value, dev).reshape(L, T).contiguous()
-                cdf = _to_device(eo.cdf, dev).contiguous()
-                self.keep += [mk, mv, cdf]
-                tc = 0
-                for dc in eo.data_chunks:
-                    if dc.bytestream.dtype != torch.uint8 or dc.bytestream.dim() != 1:
-                        raise RuntimeError("bytestream must be a 1-D uint8 tensor")
-                    if dc.bytestream_lengths.dtype != torch.int32 or dc.bytestream_lengths.numel() != NL * C:
-                        raise RuntimeError("bytestream_lengths must be int32 [2L, C]")
-                    if not 0 < dc.ntokens <= CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK:
-                        raise RuntimeError("a sub-chunk holds 1..256 tokens")
-                    bs = _to_device(dc.bytestream, dev).contiguous()
-                    ln = _to_device(dc.bytestream_lengths, dev).contiguous()
-                    self.keep += [bs, ln]
-                    self.payload_bytes += bs.numel()
-                    job = _lib.DecodeJob()
-                    job.cdf = cdf.data_ptr()
-                    job.bytes = bs.data_ptr()
-                    job.lengths = ln.data_ptr()
-                    job.group_off = goff.data_ptr() + 8 * len(jobs_all) * ngroups
-                    job.scales_k = mk.data_ptr() + mk.element_size() * tc
-                    job.scales_v = mv.data_ptr() + mv.element_size() * tc
-                    job.out = out.data_ptr() + esz * (t0 + tc) * o_token
-                    job.nbytes = bs.numel()
-                    job.ntokens = dc.ntokens
-                    job.scale_stride = T
-                    jobs_all.append(job)
-                    tc += dc.ntokens
-                t0 += T
+        for v in views:
+            self.keep += v.keep
+            self.table_bytes += v.table_bytes
+            self.length_bytes += v.length_bytes
+            tc = 0
+            for bs, ln, ntok in v.subs:
+                self.payload_bytes += bs.numel()
+                job = _lib.DecodeJob()
+                job.tables = v.tables.data_ptr()
+                job.bytes = bs.data_ptr()
+                job.lengths = ln.data_ptr()
+                job.group_off = goff.data_ptr() + 8 * len(jobs_all) * ngroups
+                job.scales_k = v.mk.data_ptr() + v.mk.element_size() * tc
+                job.scales_v = v.mv.data_ptr() + v.mv.element_size() * tc
+                job.out = out.data_ptr() + esz * (t0 + tc) * o_token
+                job.table_row_off = row_off.data_ptr() if v.table_kind == _lib.CG_TABLES_COUNTS else None
+                job.nbytes = bs.numel()
+                job.ntokens = ntok
+                job.scale_stride = v.T
+                job.table_kind = v.table_kind
+                job.length_kind = v.length_kind
+                jobs_all.append(job)
+                tc += ntok
+            t0 += v.T
         self.batches = []
         for b in range(0, njobs_total, _lib.CG_MAX_DECODE_JOBS):
             batch = jobs_all[b:b + _lib.CG_MAX_DECODE_JOBS]
@@ -178,8 +244,6 @@ class DecodePlan:
         self.dtypes = (_DTYPES[scale_dtype], _DTYPES[out_dtype])
         self.njobs = njobs_total
         # bytes one decode pass must move: 16-bit KV out, payload, tables, lengths, scales in
-        self.table_bytes = sum(eo.cdf.numel() * 2 for eo in encoder_outputs)
-        self.length_bytes = njobs_total * NL * C * 4
         self.scale_bytes = NL * total_T * 2
         self.output_bytes = NL * total_T * C * esz
 
@@ -227,7 +291,7 @@ def decode_many(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Ten
     shape [L,2,T,H,D] ("vllm") or [L,2,H,T,D] ("huggingface"), T the total token count -- what
     LMCacheEngine.retrive builds with torch.cat from per-chunk from_bytes calls
     (LMCache/lmcache/cache_engine.py:282-320 in the reference).  All sub-chunks of all chunks go
-    through cg_decode_offsets + cg_decode_dequant in batches of up to 48 per launch.
+    through cg_decode_offsets + cg_decode_dequant in batches of up to 40 per launch.
 
     The chunks' tensors may live on the GPU or in (pinned) host memory; host tensors are copied to the
     GPU on the current stream first.  bins: float32 [2L] on the GPU (key bins then value bins).
@@ -240,6 +304,10 @@ def decode_many(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Ten
 _copy_streams = {}
 
 
+def _chunk_tokens(eo) -> int:
+    return eo.num_tokens if isinstance(eo, flat_format.FlatChunk) else eo.max_tensors_key.shape[1]
+
+
 def decode_many_pipelined(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Tensor, fmt: str,
                           out_dtype: torch.dtype, out: torch.Tensor = None, groups: int = 4,
                           workspaces: list = None) -> torch.Tensor:
@@ -249,13 +317,12 @@ def decode_many_pipelined(encoder_outputs: List[CacheGenGPUEncoderOutput], bins:
     n = len(encoder_outputs)
     groups = max(1, min(groups, n))
     first = encoder_outputs[0]
-    dev = first.cdf.device if first.cdf.is_cuda else torch.device("cuda", torch.cuda.current_device())
-    if groups == 1 or first.cdf.is_cuda:
+    dev = _device_of(first) if _on_gpu(first) else torch.device("cuda", torch.cuda.current_device())
+    if groups == 1 or _on_gpu(first):
         return decode_many(encoder_outputs, bins, fmt, out_dtype, out=out,
                            workspace=workspaces[0] if workspaces else None)
-    NL, C, _ = first.cdf.shape
-    L, H, D = NL // 2, first.num_heads, first.head_size
-    total_T = sum(eo.max_tensors_key.shape[1] for eo in encoder_outputs)
+    L, H, D = bins.numel() // 2, first.num_heads, first.head_size
+    total_T = sum(_chunk_tokens(eo) for eo in encoder_outputs)
     shape = (L, 2, total_T, H, D) if fmt == "vllm" else (L, 2, H, total_T, D)
     if out is None:
         out = torch.empty(shape, dtype=out_dtype, device=dev)
@@ -275,7 +342,7 @@ def decode_many_pipelined(encoder_outputs: List[CacheGenGPUEncoderOutput], bins:
         part = encoder_outputs[g * per:(g + 1) * per]
         if not part:
             break
-        tg = sum(eo.max_tensors_key.shape[1] for eo in part)
+        tg = sum(_chunk_tokens(eo) for eo in part)
         view = out[:, :, t0:t0 + tg] if fmt == "vllm" else out[:, :, :, t0:t0 + tg]
         with torch.cuda.stream(copy_stream):
             plan = DecodePlan(part, bins, fmt, out_dtype, out=view, workspace=workspaces[g], device=dev)
@@ -319,19 +386,19 @@ class CacheGenDeserializer(Deserializer):
 
     def decode(self, encoder_output: CacheGenGPUEncoderOutput, out: torch.Tensor = None) -> torch.Tensor:
         """`from_bytes` without the unpickling."""
-        ntokens = encoder_output.max_tensors_key.shape[1]
+        ntokens = _chunk_tokens(encoder_output)
         if ntokens > self.chunk_size:
             # the reference slices a chunk_size-row buffer and fails in its reshape (dec.py:138-141,101)
             raise RuntimeError(f"blob holds {ntokens} tokens, more than chunk_size = {self.chunk_size}")
-        return decode_to_kv(encoder_output, self._bins_on(encoder_output.cdf.device), self.fmt, self.out_dtype,
+        return decode_to_kv(encoder_output, self._bins_on(_device_of(encoder_output)), self.fmt, self.out_dtype,
                             out=out, workspace=self._workspace)
 
     def decode_many(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None) -> torch.Tensor:
         """Consecutive chunks of one KV cache into one blob, in as few launches as possible."""
         for eo in encoder_outputs:
-            if eo.max_tensors_key.shape[1] > self.chunk_size:
+            if _chunk_tokens(eo) > self.chunk_size:
                 raise RuntimeError(f"a blob holds more tokens than chunk_size = {self.chunk_size}")
-        return decode_many(encoder_outputs, self._bins_on(encoder_outputs[0].cdf.device), self.fmt, self.out_dtype,
+        return decode_many(encoder_outputs, self._bins_on(_device_of(encoder_outputs[0])), self.fmt, self.out_dtype,
                            out=out, workspace=self._workspace)
 
     def decode_many_host(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None,
@@ -340,7 +407,7 @@ class CacheGenDeserializer(Deserializer):
         ws = self._workspace.setdefault("groups", [dict() for _ in range(groups)])
         if len(ws) < groups:
             ws += [dict() for _ in range(groups - len(ws))]
-        return decode_many_pipelined(encoder_outputs, self._bins_on(encoder_outputs[0].cdf.device), self.fmt,
+        return decode_many_pipelined(encoder_outputs, self._bins_on(_device_of(encoder_outputs[0])), self.fmt,
                                      self.out_dtype, out=out, groups=groups, workspaces=ws)
 
     def group_status_words(self):
@@ -349,7 +416,7 @@ class CacheGenDeserializer(Deserializer):
 
     def plan(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None) -> DecodePlan:
         """The launch plan decode_many would run, for callers that decode the same chunks repeatedly."""
-        return DecodePlan(encoder_outputs, self._bins_on(encoder_outputs[0].cdf.device), self.fmt, self.out_dtype,
+        return DecodePlan(encoder_outputs, self._bins_on(_device_of(encoder_outputs[0])), self.fmt, self.out_dtype,
                           out=out, workspace=self._workspace)
 
     def _bins_on(self, dev) -> torch.Tensor:
@@ -369,5 +436,7 @@ class CacheGenDeserializer(Deserializer):
                 raise RuntimeError("cachegen decode: " + _lib.status_text(bits))
 
     def from_bytes(self, bs: bytes) -> torch.Tensor:
+        if flat_format.is_flat(bs):
+            return self.decode(flat_format.from_bytes(bs))  # a CGB2 container: one copy to the GPU, decoded in place
         # tensors pickled on a GPU come back on that GPU; anything else is staged by the decode plan
         return self.decode(CacheGenGPUEncoderOutput.from_bytes(bs))

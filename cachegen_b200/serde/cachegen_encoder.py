@@ -18,6 +18,7 @@ import torch
 from .. import _lib
 from ..config import LMCacheEngineConfig, LMCacheEngineMetadata
 from . import cachegen_basics as CGBasics
+from . import flat_format
 from .cachegen_basics import CacheGenConfig, CacheGenGPUBytestream, CacheGenGPUEncoderOutput
 from .serde import Serializer
 
@@ -38,13 +39,16 @@ def _split_kv(tensor: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return torch.unbind(tensor.reshape(num_layers, 2, num_tokens, num_heads * head_size), dim=1)
 
 
-def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor, max_bins: int):
+def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor, max_bins: int,
+                        with_counts: bool = False):
     """Fused torch_quant_vectorized (K and V) + calculate_cdf (K and V) + the two torch.cat of
     encode_function (enc.py:42-59, 257-267).
 
     kv: CUDA fp16/bf16 blob addressed as [L, 2, T, H, D] (any strides with a unit innermost stride, so
         the permuted view of a "huggingface" blob is read in place).
-    Returns (symbols int8 [2L, T, C], scales [2L, T] in kv.dtype, tables int16 [2L, C, max_bins + 1]).
+    Returns (symbols int8 [2L, T, C], scales [2L, T] in kv.dtype, tables int16 [2L, C, max_bins + 1]);
+    with_counts adds (byte counts uint8 of the compact table form, int32 status word whose
+    CG_S_COUNT_OVERFLOW bit says they are unusable for this chunk).
     """
     if kv.dim() != 5 or kv.shape[1] != 2:
         raise RuntimeError(f"expected a KV blob of shape [L, 2, T, H, D], got {tuple(kv.shape)}")
@@ -63,20 +67,32 @@ def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: to
     sym = torch.empty((2 * L, T, C), dtype=torch.int8, device=dev)
     scales = torch.empty((2 * L, T), dtype=kv.dtype, device=dev)
     cdf = torch.empty((2 * L, C, max_bins + 1), dtype=torch.int16, device=dev)
+    counts = row_off = status = None
+    if with_counts:
+        offs = flat_format.table_row_offsets(bins.cpu(), C)
+        row_off = torch.tensor(offs, dtype=torch.int64, device=dev)
+        counts = torch.empty(offs[-1], dtype=torch.uint8, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+    null = ctypes.c_void_p(None)
     with torch.cuda.device(dev):
         rc = _lib.lib().cg_quantize_cdf(_ptr(kv), _DTYPES[kv.dtype], kv.stride(0), kv.stride(1), kv.stride(2),
                                         kv.stride(3), L, T, H, D, _ptr(bins), int(max_bins), _ptr(sym),
-                                        _ptr(scales), _ptr(cdf), _stream(dev))
+                                        _ptr(scales), _ptr(cdf), _ptr(counts) if with_counts else null,
+                                        _ptr(row_off) if with_counts else null, _ptr(status) if with_counts else null,
+                                        _stream(dev))
     _lib.check(rc, "cg_quantize_cdf")
+    if with_counts:
+        return sym, scales, cdf, counts, status
     return sym, scales, cdf
 
 
-def encode_streams(cdf: torch.Tensor, sym: torch.Tensor, scratch_stride: int = None):
+def encode_streams(cdf: torch.Tensor, sym: torch.Tensor, scratch_stride: int = None, extra_status: torch.Tensor = None):
     """The sub-chunk loop of encode_function in one pass (enc.py:269-292).
 
     cdf int16 [2L, C, Lp], sym int8 [2L, T, C] contiguous.  Returns (bytes uint8 [total], lengths int32
     [nsub, 2L, C], sub_off: python list of nsub+1 byte offsets of the sub-chunks inside `bytes`).
-    Synchronises once, to size the output.
+    Synchronises once, to size the output; `extra_status` (an int32 word) is read in the same transfer
+    and its value appended to the result.
     """
     NL, T, C = sym.shape
     lp = cdf.shape[2]
@@ -95,15 +111,18 @@ def encode_streams(cdf: torch.Tensor, sym: torch.Tensor, scratch_stride: int = N
         rc = L.cg_encode_chunk(_ptr(cdf), _ptr(sym), NL, T, C, lp, _ptr(scratch), stride, _ptr(lengths),
                                _ptr(group_off), _ptr(sub_off), _ptr(status), _stream(dev))
         _lib.check(rc, "cg_encode_chunk")
-        host = torch.cat((sub_off, status.to(torch.int64))).cpu()  # the one synchronisation
-        bits = int(host[-1])
+        words = [sub_off, status.to(torch.int64)] + ([extra_status.to(torch.int64)] if extra_status is not None else [])
+        host = torch.cat(words).cpu()  # the one synchronisation
+        bits = int(host[nsub + 1])
         if bits:
             raise RuntimeError("cachegen encode: " + _lib.status_text(bits))
-        offs = [int(v) for v in host[:-1]]
+        offs = [int(v) for v in host[:nsub + 1]]
         out = torch.empty(offs[-1], dtype=torch.uint8, device=dev)
         rc = L.cg_compact_streams(_ptr(scratch), stride, _ptr(lengths), _ptr(group_off), _ptr(sub_off), nsub, NL,
                                   C, _ptr(out), _stream(dev))
         _lib.check(rc, "cg_compact_streams")
+    if extra_status is not None:
+        return out, lengths, offs, int(host[nsub + 2])
     return out, lengths, offs
 
 
@@ -137,12 +156,47 @@ def encode_function(kv: torch.Tensor, config: CacheGenConfig, key_bins: torch.Te
         num_heads=num_heads, head_size=head_size)
 
 
+def encode_flat(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor,
+                compact_tables: bool = True) -> flat_format.FlatChunk:
+    """Encodes one chunk of KV, [L, 2, T, H, D] on the GPU, into a CGB2 container on the GPU
+    (flat_format.py): the same tables, lengths and streams as encode_function, with uint16 lengths and,
+    when every non-centre histogram count fits a byte, the tables as byte counts."""
+    L, _, T, H, D = kv.shape
+    C = H * D
+    kmax, vmax = int(key_bins.max()), int(value_bins.max())
+    if kmax != vmax:
+        raise RuntimeError(f"Sizes of tensors must match: key tables have {kmax + 1} entries, value tables {vmax + 1}")
+    sym, scales, cdf, counts, qstatus = quantize_and_tables(kv, key_bins, value_bins, kmax, with_counts=True)
+    stream_bytes, lengths, offs, qbits = encode_streams(cdf, sym, extra_status=qstatus)
+    use_counts = compact_tables and not (qbits & _lib.CG_S_COUNT_OVERFLOW)
+    tables = counts if use_counts else cdf.view(torch.uint8).reshape(-1)
+    header = flat_format.layout(L, H, D, T, kmax + 1, kv.dtype,
+                                flat_format.TABLES_COUNTS if use_counts else flat_format.TABLES_CDF,
+                                tables.numel(), flat_format.LENGTHS_U16, offs)
+    blob = torch.empty(header.total, dtype=torch.uint8, device=kv.device)
+    head = header.pack()
+    blob[:len(head)].copy_(torch.frombuffer(bytearray(head), dtype=torch.uint8), non_blocking=True)
+    chunk = flat_format.FlatChunk(blob, header)
+    chunk.scales().copy_(scales)
+    blob[header.off_tables:header.off_tables + tables.numel()].copy_(tables)
+    n = 2 * L * C
+    blob[header.off_lengths:header.off_lengths + len(offs[:-1]) * n * 2].view(torch.int16).copy_(
+        lengths.reshape(-1).to(torch.int16))  # at most 520: fits
+    blob[header.off_payload:header.off_payload + offs[-1]].copy_(stream_bytes)
+    return chunk
+
+
 class CacheGenSerializer(Serializer):
     """Reference: enc.py:303-348.  `cachegen_config` may be given instead of looking it up from
-    metadata.model_name (quality levels other than the built-in ones)."""
+    metadata.model_name (quality levels other than the built-in ones).  wire_format: "pickle" (the
+    reference's blob, default) or "flat" (the CGB2 container of flat_format.py, which the reference
+    cannot read)."""
 
     def __init__(self, config: LMCacheEngineConfig, metadata: LMCacheEngineMetadata,
-                 cachegen_config: CacheGenConfig = None):
+                 cachegen_config: CacheGenConfig = None, wire_format: str = "pickle"):
+        if wire_format not in ("pickle", "flat"):
+            raise ValueError(f"unknown wire format {wire_format!r}")
+        self.wire_format = wire_format
         _lib.lib()  # fail at construction if the CUDA library is missing
         self.cachegen_config = cachegen_config or CacheGenConfig.from_model_name(metadata.model_name)
         self.chunk_size = config.chunk_size
@@ -163,6 +217,18 @@ class CacheGenSerializer(Serializer):
         ntokens = tensor.shape[2]
         return encode_function(tensor.cuda(), self.cachegen_config, self.key_bins, self.value_bins, ntokens)
 
+    def encode_flat(self, tensor: torch.Tensor, compact_tables: bool = True) -> flat_format.FlatChunk:
+        """The chunk as a CGB2 container on the GPU."""
+        if self.fmt == "huggingface":
+            tensor = tensor.permute(0, 1, 3, 2, 4)
+        tensor = tensor.cuda()
+        if tensor.stride(4) != 1:
+            tensor = tensor.contiguous()
+        return encode_flat(tensor, self.key_bins, self.value_bins, compact_tables)
+
     def to_bytes(self, tensor: torch.Tensor) -> bytes:
-        """KV blob ([L,2,T,H,D] for "vllm", [L,2,H,T,D] for "huggingface") -> pickled bytes (enc.py:324-348)."""
+        """KV blob ([L,2,T,H,D] for "vllm", [L,2,H,T,D] for "huggingface") -> bytes (enc.py:324-348):
+        the reference's pickle, or a CGB2 container when wire_format == "flat"."""
+        if self.wire_format == "flat":
+            return self.encode_flat(tensor).tobytes()
         return self.encode(tensor).to_bytes()

@@ -46,7 +46,22 @@ extern "C" {
 /* channels of one row handled by one thread block (one thread per stream) */
 #define CG_GROUP_CHANNELS 128
 /* sub-chunks one fused decode launch can take */
-#define CG_MAX_DECODE_JOBS 48
+#define CG_MAX_DECODE_JOBS 40
+
+/* Table kinds of cg_decode_job.tables.
+ * CG_TABLES_CDF:    int16 [nrows, nchannels, lp], the reference's tables (calculate_cdf).
+ * CG_TABLES_COUNTS: the histograms the tables are built from, one byte per (row, non-centre symbol,
+ *   channel): row r has 2*Cq_r stored symbols (Cq_r = bins_r // 2 - 1; symbols 0..2*Cq_r except the
+ *   centre symbol Cq_r, whose count is the chunk's token count minus the others), laid out as
+ *   counts[table_row_off[r] + j * nchannels + channel], j = symbol index with the centre skipped,
+ *   table_row_off[r] = nchannels * sum of 2*Cq over the rows before r.  The decoder rebuilds
+ *   cdf[i] = (uint16)((0xFFFF - max_bins) * #{sym < i} / ntokens) + i from them (cal_cdf.cu:11-15,40-49):
+ *   a table costs 14 or 30 bytes instead of 66.  Usable when no non-centre count exceeds 255.
+ * Length kinds of cg_decode_job.lengths: CG_LENGTHS_I32 (the reference's int32) or CG_LENGTHS_U16. */
+#define CG_TABLES_CDF 0
+#define CG_TABLES_COUNTS 1
+#define CG_LENGTHS_I32 0
+#define CG_LENGTHS_U16 1
 
 /* argument errors (returned) */
 #define CG_OK 0
@@ -64,6 +79,7 @@ extern "C" {
 #define CG_S_STREAM_OVERFLOW 1 /* an encoded stream needed more bytes than its scratch row */
 #define CG_S_BAD_LENGTHS 2     /* negative length, or lengths reach past the byte array */
 #define CG_S_BAD_SYMBOL 4      /* a symbol outside [0, Lp-2] was met while encoding */
+#define CG_S_COUNT_OVERFLOW 8  /* a histogram count above 255: the byte-count tables are not usable */
 
 const char *cg_version(void);
 const char *cg_status_string(int code);
@@ -136,11 +152,14 @@ int cg_decode_prefsum(const int16_t *cdf, const uint8_t *bytes, int64_t nbytes,
  *     then max_tensors_value, same dtype as kv);  cdf_out: int16 [2L, C, max_bins+1].
  * The reference builds key and value tables with their own max_bins and concatenates them,
  * which only works when both are equal (cachegen_encoder.py:265-267); pass that one value.
+ * counts_out (may be NULL): the CG_TABLES_COUNTS form of the same tables, with table_row_off [2L]
+ *     as described there; CG_S_COUNT_OVERFLOW is raised in *status when a count does not fit a byte.
  */
 int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
                     int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
                     const float *bins, int max_bins, int8_t *sym_out, void *scales_out,
-                    int16_t *cdf_out, void *stream);
+                    int16_t *cdf_out, uint8_t *counts_out, const int64_t *table_row_off,
+                    int32_t *status, void *stream);
 
 /*
  * Replaces the sub-chunk loop of encode_function: encode_fast_new + the length bookkeeping of
@@ -175,9 +194,9 @@ int cg_compact_streams(const uint8_t *scratch, int64_t scratch_stride, const int
 
 /* One sub-chunk (CacheGenGPUBytestream, cachegen_basics.py:124-131) of one encoded chunk. */
 typedef struct cg_decode_job {
-    const int16_t *cdf;      /* [nrows, nchannels, lp] table set of the chunk */
+    const void *tables;      /* table set of the chunk, see table_kind */
     const uint8_t *bytes;    /* the sub-chunk's streams, back to back */
-    const int32_t *lengths;  /* [nrows, nchannels] stream lengths (bytestream_lengths) */
+    const void *lengths;     /* [nrows, nchannels] stream lengths (bytestream_lengths), see length_kind */
     const int64_t *group_off;/* [nrows*ceil(nchannels/128)] exclusive byte offset of each
                                 128-channel group inside `bytes`: written by cg_decode_offsets */
     const void *scales_k;    /* 16-bit [nlayers, scale_stride]: max_tensors_key, at this
@@ -185,9 +204,13 @@ typedef struct cg_decode_job {
     const void *scales_v;    /* 16-bit [nlayers, scale_stride]: max_tensors_value, likewise */
     void *out;               /* 16-bit KV, element (layer 0, key, this sub-chunk's first token,
                                 head 0, d 0) of the output blob */
+    const int64_t *table_row_off; /* CG_TABLES_COUNTS only: [nrows] row offsets into `tables` */
     int64_t nbytes;          /* size of `bytes` */
     int32_t ntokens;         /* tokens in this sub-chunk, 1..256 */
-    int32_t scale_stride;    /* elements between consecutive layers in scales_k / scales_v */
+    int32_t scale_stride;    /* elements between consecutive layers in scales_k / scales_v
+                                (= the chunk's token count, over which its tables were built) */
+    int32_t table_kind;      /* CG_TABLES_CDF or CG_TABLES_COUNTS */
+    int32_t length_kind;     /* CG_LENGTHS_I32 or CG_LENGTHS_U16 */
 } cg_decode_job;
 
 /*

@@ -52,12 +52,13 @@ def test_argument_errors_need_no_gpu(lib):
     assert lib.cg_decode_prefsum(one, one, 8, None, one, s3, 1, 1, 1, 33, None, None) == -1
     assert lib.cg_decode_prefsum(one, one, 8, one, one, s3, 1, 300, 1, 33, None, None) == -3
     assert lib.cg_decode_padded(one, one, 0, one, one, s3, 1, 1, 1, 33, None, None) == -2
-    assert lib.cg_quantize_cdf(one, 7, 1, 1, 1, 1, 1, 1, 1, 1, one, 32, one, one, one, None) == -7
-    assert lib.cg_quantize_cdf(one, 0, 1, 1, 1, 1, 1, 70000, 1, 1, one, 32, one, one, one, None) == -9
+    assert lib.cg_quantize_cdf(one, 7, 1, 1, 1, 1, 1, 1, 1, 1, one, 32, one, one, one, None, None, None, None) == -7
+    assert lib.cg_quantize_cdf(one, 0, 1, 1, 1, 1, 1, 70000, 1, 1, one, 32, one, one, one, None, None, None, None) == -9
+    assert lib.cg_quantize_cdf(one, 0, 1, 1, 1, 1, 1, 16, 1, 1, one, 32, one, one, one, one, None, None, None) == -1
     assert lib.cg_encode_chunk(one, one, 1, 1, 1, 33, one, 10, one, one, one, None, None) == -5
     assert lib.cg_compact_streams(one, 8, one, one, one, 0, 1, 1, one, None) == -2
     jobs = (_lib.DecodeJob * 1)()
-    assert lib.cg_decode_offsets(jobs, 49, 1, 1, one, None, None) == -6
+    assert lib.cg_decode_offsets(jobs, 41, 1, 1, one, None, None) == -6
     assert lib.cg_decode_offsets(jobs, 1, 1, 1, one, None, None) == -1   # job.lengths is NULL
     assert lib.cg_decode_dequant(jobs, 1, 1, 1, 1, 33, one, 0, 5, 1, 1, 1, 1, None, None) == -7
     assert lib.cg_decode_dequant(jobs, 1, 1, 1, 1, 33, one, 0, 0, 1, 1, 1, 1, None, None) == -1

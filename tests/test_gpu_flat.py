@@ -1,0 +1,100 @@
+"""The CGB2 container on the GPU: decoding it gives bit for bit what decoding the reference-format
+blob of the same chunk gives, with both table forms, and the byte-count form falls back to full tables
+when a count does not fit a byte."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import bits_np, kv_rows
+from test_gpu_serde import MODEL_7B, make_serde, oracle_encode
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("fmt,dtype,T", [("vllm", torch.float16, 700), ("huggingface", torch.bfloat16, 256),
+                                         ("vllm", torch.bfloat16, 37)])
+def test_flat_container_decodes_like_the_pickle_blob(oracle, fmt, dtype, T):
+    from cachegen_b200.serde import flat_format as ff
+    from cachegen_b200.synth import generate_kv
+    L, H, D = 32, 4, 64
+    kv = generate_kv(L, H, D, T, seed=T, device="cpu", dtype=dtype).cuda()
+    blob_kv = kv if fmt == "vllm" else kv.permute(0, 1, 3, 2, 4).contiguous()
+    ser, de = make_serde(1024, fmt, out_dtype=torch.float16)
+    want = de.decode(ser.encode(blob_kv))
+    sizes = {}
+    for compact in (True, False):
+        chunk = ser.encode_flat(blob_kv, compact_tables=compact)
+        # tables over more than 255 tokens can hold counts that do not fit a byte: full tables then
+        assert chunk.header.table_kind == (ff.TABLES_COUNTS if compact and T <= 256 else ff.TABLES_CDF)
+        assert chunk.header.length_kind == ff.LENGTHS_U16 and chunk.header.nsub == (T + 255) // 256
+        got = de.decode(chunk)
+        de.check_status()
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+        sizes[compact] = chunk.header.total
+        # through bytes, and from pinned host memory
+        raw = chunk.tobytes()
+        assert ff.is_flat(raw) and len(raw) == chunk.header.total
+        assert torch.equal(de.from_bytes(raw).view(torch.int16), want.view(torch.int16))
+        assert torch.equal(de.decode(chunk.pin_memory()).view(torch.int16), want.view(torch.int16))
+    assert sizes[True] < sizes[False] or T > 256
+    # streams in the container are the oracle's
+    if fmt == "vllm" and dtype == torch.float16:
+        ref = oracle_encode(oracle, kv.cpu(), ser.key_bins.cpu().numpy(), ser.value_bins.cpu().numpy(), oracle.F16)
+        chunk = ser.encode_flat(blob_kv)
+        for j, (want_bytes, want_len) in enumerate(ref["chunks"]):
+            assert chunk.payload(j).cpu().numpy().tobytes() == want_bytes.tobytes()
+            assert (chunk.lengths(j).cpu().numpy().view(np.uint16) == want_len).all()
+        assert (bits_np(chunk.scales()) == ref["max"].reshape(2 * L, T)).all()
+
+
+def test_flat_serializer_wire_format_and_mixed_batches():
+    from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
+    from cachegen_b200.serde import CacheGenSerializer
+    from cachegen_b200.synth import generate_kv
+    kv = generate_kv(32, 2, 128, 512, seed=9, device="cuda", dtype=torch.float16)
+    ser, de = make_serde(256, "vllm", out_dtype=torch.float16)
+    config = LMCacheEngineConfig.from_defaults(chunk_size=256)
+    meta = LMCacheEngineMetadata(model_name=MODEL_7B, world_size=1, worker_id=0, fmt="vllm")
+    flat_ser = CacheGenSerializer(config, meta, wire_format="flat")
+    a, b = kv[:, :, :256], kv[:, :, 256:]
+    blob = flat_ser.to_bytes(a)
+    assert blob[:4] == b"CGB2"
+    want = torch.cat((de.decode(ser.encode(a)), de.decode(ser.encode(b))), dim=2)
+    assert torch.equal(de.from_bytes(blob), want[:, :, :256])
+    # one call, one chunk in each container
+    got = de.decode_many([ser.encode(a), flat_ser.encode_flat(b)])
+    assert torch.equal(got, want)
+    got = de.decode_many_host([flat_ser.encode_flat(a).pin_memory(), flat_ser.encode_flat(b).pin_memory()], groups=2)
+    de.check_status()
+    assert torch.equal(got, want)
+
+
+def test_byte_counts_fall_back_when_a_count_overflows():
+    """A channel that sits at the row maximum for all 256 tokens has 256 occurrences of a non-centre
+    symbol: the byte-count tables cannot hold that, so the container carries full tables."""
+    from cachegen_b200.serde import flat_format as ff
+    g = torch.Generator().manual_seed(3)
+    L, H, D, T = 32, 1, 128, 256
+    kv = torch.randn(L, 2, T, H, D, generator=g).clamp(-2, 2).to(torch.float16)
+    kv[5, 0, :, 0, 7] = 3.0  # always the largest value of its token row -> always the top symbol
+    kv = kv.cuda()
+    ser, de = make_serde(256, "vllm", out_dtype=torch.float16)
+    chunk = ser.encode_flat(kv)
+    assert chunk.header.table_kind == ff.TABLES_CDF
+    want = de.decode(ser.encode(kv))
+    assert torch.equal(de.decode(chunk), want)
+    kv[5, 0, 100, 0, 7] = 0.0  # 255 + 1: fits again
+    chunk = ser.encode_flat(kv)
+    assert chunk.header.table_kind == ff.TABLES_COUNTS
+    assert torch.equal(de.decode(chunk), de.decode(ser.encode(kv)))
+
+
+def test_mismatched_bins_are_refused_not_misread():
+    from cachegen_b200.serde.cachegen_basics import CacheGenConfig
+    from cachegen_b200.synth import generate_kv
+    kv = generate_kv(32, 1, 128, 64, seed=1, device="cuda", dtype=torch.float16)
+    half = CacheGenConfig.from_model_name(MODEL_7B).with_bins_divided(2)
+    ser, _ = make_serde(256, "vllm", cachegen_config=half)
+    _, de_full = make_serde(256, "vllm")
+    with pytest.raises(RuntimeError):
+        de_full.decode(ser.encode_flat(kv))  # 17-entry tables against a 33-entry configuration's counts

@@ -63,9 +63,9 @@ def test_static_workspace_decode_matches_workspace_decode_twice():
 def test_static_workspace_rejects_oversized_requests():
     from cachegen_b200 import _lib
     lib = _lib.lib()
-    jobs = (_lib.DecodeJob * 48)()
+    jobs = (_lib.DecodeJob * 40)()
     one = ctypes.c_void_p(16)  # never dereferenced: the call is rejected before anything is launched
-    # 48 jobs x 2*160 rows x 64 groups of 128 channels = 983,040 entries > 131,072
-    rc = lib.cg_decode_dequant_static(jobs, 48, 160, 64, 128, 33, one, 0, 0, 1, 1, 1, 1, None, None)
+    # 40 jobs x 2*160 rows x 64 groups of 128 channels = 819,200 entries > 131,072
+    rc = lib.cg_decode_dequant_static(jobs, 40, 160, 64, 128, 33, one, 0, 0, 1, 1, 1, 1, None, None)
     assert rc == -6
     assert b"workspace" in lib.cg_status_string(rc)
