@@ -183,10 +183,6 @@ struct BitWindow {
 };
 
 // ---- decode loop ------------------------------------------------------------------------------------------
-#ifndef CG_DEC_VARIANT
-#define CG_DEC_VARIANT 0
-#endif
-
 // Scaled table entry for the current span: (span * c16) >> 32 with span32 = span mod 2^32, which is 0
 // exactly when the range is the full 2^32 (then the product is c16 itself).
 CG_HD uint32_t scale_exact(uint32_t span32, uint32_t c16) { return span32 ? cg_umulhi(span32, c16) : c16; }
@@ -287,9 +283,6 @@ CG_HD void decode_stream(Smem sm, uint32_t col, int maxsym, const uint8_t *strea
         r_lo = sm.ld(col + kHalf);
         r_hi = sm.ld(col + kTop + kHalf);
     }
-#if defined(__CUDA_ARCH__) && (CG_DEC_VARIANT & 2)
-#pragma unroll 2
-#endif
     for (int left = ntok - 1; left > 0; --left) {
         // rare, and taken by the whole warp: a lane is low on bits, or starts this symbol from the full range
         if (cg_any_lane(lanes, bw.low_water() || (kFast && st.span32 == 0u)) || !kFast) {

@@ -132,10 +132,8 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
     // because a - col is a multiple of 512
     uint32_t lut_k = smem_addr(lut) - (col >> 7), sc_a = smem_addr(scale_f);
     int ntok_r = ntok;
-#if !(CG_DEC_VARIANT & 1)
     // keep the loop's invariants in registers instead of re-deriving them from kernel parameters
     asm volatile("" : "+l"(o_token), "+r"(lut_k), "+r"(sc_a), "+r"(ntok_r));
-#endif
     auto emit = [&](uint32_t a) {
         // ((sym - Cq) / Cq) * max in fp32, then one round-to-nearest cast (cachegen_decoder.py:30-33,171-173)
         const float v = __fmul_rn(ldsf32((a >> 7) + lut_k), ldsf32(sc_a));
