@@ -188,3 +188,31 @@ def test_full_size_chunk_properties():
     err = (kv_rows(out).float() - kv_rows(kv).float()).abs()
     # half a quantisation step, plus the rounding of the result to fp16 (half an ulp at the row maximum)
     assert (err <= 0.5 * step * 1.001 + step * cq[:, None, None] * 2.0 ** -10 + 1e-6).all()
+
+
+def test_benchmark_config_one_full_round_trip_against_the_oracle(oracle):
+    """BASELINE configuration 1 at full size: Llama-7B shape (32 layers x 32 heads x 128, fp16), 1,024
+    tokens, seed 0, 7B-default bins, one serializer call per 256 tokens.  Every table, length and
+    stream byte and every decoded fp16 value is compared with the CPU oracle (2.7e8 symbols)."""
+    from cachegen_b200.synth import WORKLOADS, generate_kv
+    spec = WORKLOADS["llama7b-1k"]
+    L, H, D, T = spec["num_layers"], spec["num_heads"], spec["head_size"], spec["num_tokens"]
+    kv = generate_kv(L, H, D, T, spec["seed"], key_rho=spec["key_rho"], device="cpu", dtype=torch.float16)
+    ser, de = make_serde(256, "vllm", model=spec["model_name"], out_dtype=torch.float16)
+    kb, vb = ser.key_bins.cpu().numpy(), ser.value_bins.cpu().numpy()
+    chunks = []
+    for s in range(0, T, 256):
+        part = kv[:, :, s:s + 256].contiguous()
+        eo = ser.encode(part.cuda())
+        ref = oracle_encode(oracle, part, kb, vb, oracle.F16)
+        assert (eo.cdf.cpu().numpy() == ref["cdf"]).all()
+        want_bytes, want_len = ref["chunks"][0]
+        assert (eo.data_chunks[0].bytestream_lengths.cpu().numpy() == want_len).all()
+        assert eo.data_chunks[0].bytestream.cpu().numpy().tobytes() == want_bytes.tobytes()
+        chunks.append((eo, ref))
+    out = de.decode_many([c[0] for c in chunks])
+    de.check_status()
+    assert tuple(out.shape) == (L, 2, T, H, D)
+    for i, (_, ref) in enumerate(chunks):
+        want = oracle.dequantize(ref["sym"].view(np.uint8), ref["bins"], ref["max"], oracle.F16, oracle.F16)
+        assert (bits_np(kv_rows(out[:, :, i * 256:(i + 1) * 256])) == want).all()
