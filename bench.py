@@ -280,13 +280,12 @@ def run_ours(args, spec):
     # ---- set-up (untimed): this rank's share, encoded chunk by chunk as LMCacheEngine.store would
     kv = generate_kv(L, H, D, T, seed, key_rho=spec["key_rho"], device=dev, dtype=torch.float16, first_layer=first_layer)
     ms_encode = None
-    for attempt in range(2):  # the first pass warms the allocator (every chunk's outputs stay alive), the second is timed
-        chunks = []
+    for attempt in range(2):  # the first pass warms the allocator, the second is timed
+        chunks = None
         torch.cuda.synchronize()
         enc0, enc1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         enc0.record()
-        for s in range(0, T, CHUNK_TOKENS):
-            chunks.append(ser.encode(kv[:, :, s:s + CHUNK_TOKENS]))
+        chunks = ser.encode_many(kv, CHUNK_TOKENS, batch=16)
         enc1.record()
         torch.cuda.synchronize()
         ms_encode = enc0.elapsed_time(enc1)
@@ -417,7 +416,7 @@ def run_ours(args, spec):
         "launches_per_step": plan.launches,
         "kernel_ms": {"decode_dequant": ms_kernel, "offsets": ms_offsets},
         "encode": {"value": kv_bytes / ms_encode / 1e6, "unit": "GB/s", "ms": ms_encode,
-                   "what": "CacheGenSerializer.encode of every chunk, one call and one host sync per chunk, "
+                   "what": "CacheGenSerializer.encode_many: every chunk of the cache, one host sync per 16 chunks, "
                            "KV resident in HBM, second pass of set-up"},
         "roofline": {"bound": "hbm", "kernel": "decode_dequant_kernel", "achieved": achieved, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,

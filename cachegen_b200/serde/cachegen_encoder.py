@@ -126,6 +126,89 @@ def encode_streams(cdf: torch.Tensor, sym: torch.Tensor, scratch_stride: int = N
     return out, lengths, offs
 
 
+class _PendingChunk:
+    """One chunk whose quantise / table / coder kernels are enqueued but whose payload size is not
+    yet known on the host."""
+
+    def __init__(self, kv, key_bins, value_bins, max_bins):
+        self.L, _, self.T, self.H, self.D = kv.shape
+        self.dtype = kv.dtype
+        self.sym, self.scales, self.cdf = quantize_and_tables(kv, key_bins, value_bins, max_bins)
+        NL, T, C = self.sym.shape
+        dev = self.sym.device
+        self.nsub = (T + CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK - 1) // CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK
+        self.stride = (_lib.stream_capacity(min(T, CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK)) + 3) // 4 * 4
+        nslab = (C + _lib.CG_GROUP_CHANNELS - 1) // _lib.CG_GROUP_CHANNELS
+        self.scratch = torch.empty((self.nsub, NL * C, self.stride), dtype=torch.uint8, device=dev)
+        self.lengths = torch.empty((self.nsub, NL, C), dtype=torch.int32, device=dev)
+        self.group_off = torch.empty((self.nsub, NL * nslab), dtype=torch.int64, device=dev)
+        # sub_off[0..nsub] then the status word, so that one transfer brings both to the host
+        self.tail = torch.zeros(self.nsub + 2, dtype=torch.int64, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            rc = _lib.lib().cg_encode_chunk(_ptr(self.cdf), _ptr(self.sym), NL, T, C, self.cdf.shape[2],
+                                            _ptr(self.scratch), self.stride, _ptr(self.lengths), _ptr(self.group_off),
+                                            _ptr(self.tail), _ptr(self.status), _stream(dev))
+        _lib.check(rc, "cg_encode_chunk")
+        self.tail[self.nsub + 1:].copy_(self.status)
+        self.sym = None  # symbols are consumed; free them early
+
+    def finish(self, host_tail) -> CacheGenGPUEncoderOutput:
+        bits = int(host_tail[self.nsub + 1])
+        if bits:
+            raise RuntimeError("cachegen encode: " + _lib.status_text(bits))
+        offs = [int(v) for v in host_tail[:self.nsub + 1]]
+        dev = self.cdf.device
+        NL, C = 2 * self.L, self.H * self.D
+        pieces = [torch.empty(offs[j + 1] - offs[j], dtype=torch.uint8, device=dev) for j in range(self.nsub)]
+        with torch.cuda.device(dev):
+            if self.nsub == 1:
+                rc = _lib.lib().cg_compact_streams(_ptr(self.scratch), self.stride, _ptr(self.lengths),
+                                                   _ptr(self.group_off), _ptr(self.tail), 1, NL, C, _ptr(pieces[0]),
+                                                   _stream(dev))
+                _lib.check(rc, "cg_compact_streams")
+            else:
+                out = torch.empty(offs[-1], dtype=torch.uint8, device=dev)
+                rc = _lib.lib().cg_compact_streams(_ptr(self.scratch), self.stride, _ptr(self.lengths),
+                                                   _ptr(self.group_off), _ptr(self.tail), self.nsub, NL, C, _ptr(out),
+                                                   _stream(dev))
+                _lib.check(rc, "cg_compact_streams")
+                pieces = [out[offs[j]:offs[j + 1]].clone() for j in range(self.nsub)]
+        step = CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK
+        data_chunks = [CacheGenGPUBytestream(pieces[j], self.lengths[j] if self.nsub == 1 else self.lengths[j].clone(),
+                                             min(step, self.T - j * step)) for j in range(self.nsub)]
+        for t in (self.scratch, self.group_off, self.tail):
+            t.record_stream(torch.cuda.current_stream(dev))
+        return CacheGenGPUEncoderOutput(data_chunks, self.cdf,
+                                        max_tensors_key=self.scales[:self.L].clone().unsqueeze(-1),
+                                        max_tensors_value=self.scales[self.L:].clone().unsqueeze(-1),
+                                        num_heads=self.H, head_size=self.D)
+
+
+def encode_many(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor, chunk_tokens: int,
+                batch: int = 16) -> list:
+    """Encodes a whole KV cache [L, 2, T, H, D] (GPU, unit innermost stride) chunk by chunk, as
+    LMCacheEngine.store does with one to_bytes call per chunk (LMCache/lmcache/cache_engine.py:205-255
+    in the reference), but with one host synchronisation per `batch` chunks instead of one per chunk:
+    all kernels of a batch are enqueued first, their payload sizes come back in one transfer, then the
+    streams are gathered.  Every chunk keeps its own scratch (136 MB for a 7B-shape chunk) until then.
+    Returns the chunks' CacheGenGPUEncoderOutput objects, identical to per-chunk encode_function calls."""
+    kmax, vmax = int(key_bins.max()), int(value_bins.max())
+    if kmax != vmax:
+        raise RuntimeError(f"Sizes of tensors must match: key tables have {kmax + 1} entries, value tables {vmax + 1}")
+    T = kv.shape[2]
+    starts = list(range(0, T, chunk_tokens))
+    result = []
+    for b in range(0, len(starts), batch):
+        pending = [_PendingChunk(kv[:, :, s:s + chunk_tokens], key_bins, value_bins, kmax) for s in starts[b:b + batch]]
+        host = torch.cat([p.tail for p in pending]).cpu()  # the batch's one synchronisation
+        pos = 0
+        for p in pending:
+            result.append(p.finish(host[pos:pos + p.nsub + 2]))
+            pos += p.nsub + 2
+    return result
+
+
 def encode_function(kv: torch.Tensor, config: CacheGenConfig, key_bins: torch.Tensor, value_bins: torch.Tensor,
                     chunk_size: int) -> CacheGenGPUEncoderOutput:
     """Encodes one chunk of KV, [L, 2, T, H, D] on the GPU, T == chunk_size (enc.py:247-301)."""
@@ -216,6 +299,16 @@ class CacheGenSerializer(Serializer):
             tensor = tensor.permute(0, 1, 3, 2, 4)  # a view; the kernels read it through its strides
         ntokens = tensor.shape[2]
         return encode_function(tensor.cuda(), self.cachegen_config, self.key_bins, self.value_bins, ntokens)
+
+    def encode_many(self, tensor: torch.Tensor, chunk_tokens: int = None, batch: int = 16) -> list:
+        """A whole KV cache, one encoded chunk per `chunk_tokens` (default: the configured chunk size)
+        tokens, with one host synchronisation per `batch` chunks."""
+        if self.fmt == "huggingface":
+            tensor = tensor.permute(0, 1, 3, 2, 4)
+        tensor = tensor.cuda()
+        if tensor.stride(4) != 1:
+            tensor = tensor.contiguous()
+        return encode_many(tensor, self.key_bins, self.value_bins, chunk_tokens or self.chunk_size, batch)
 
     def encode_flat(self, tensor: torch.Tensor, compact_tables: bool = True) -> flat_format.FlatChunk:
         """The chunk as a CGB2 container on the GPU."""

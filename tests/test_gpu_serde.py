@@ -216,3 +216,24 @@ def test_benchmark_config_one_full_round_trip_against_the_oracle(oracle):
     for i, (_, ref) in enumerate(chunks):
         want = oracle.dequantize(ref["sym"].view(np.uint8), ref["bins"], ref["max"], oracle.F16, oracle.F16)
         assert (bits_np(kv_rows(out[:, :, i * 256:(i + 1) * 256])) == want).all()
+
+
+@pytest.mark.parametrize("chunk_tokens", [256, 512])
+def test_encode_many_equals_chunk_by_chunk_encode(chunk_tokens):
+    from cachegen_b200.synth import generate_kv
+    T = 700
+    kv = generate_kv(32, 2, 128, T, seed=11, device="cuda", dtype=torch.float16)
+    ser, de = make_serde(chunk_tokens, "vllm", out_dtype=torch.float16)
+    many = ser.encode_many(kv, batch=2)
+    assert len(many) == (T + chunk_tokens - 1) // chunk_tokens
+    for i, eo in enumerate(many):
+        one = ser.encode(kv[:, :, i * chunk_tokens:(i + 1) * chunk_tokens])
+        assert torch.equal(eo.cdf, one.cdf)
+        assert torch.equal(eo.max_tensors_key, one.max_tensors_key) and torch.equal(eo.max_tensors_value, one.max_tensors_value)
+        assert len(eo.data_chunks) == len(one.data_chunks)
+        for a, b in zip(eo.data_chunks, one.data_chunks):
+            assert a.ntokens == b.ntokens and torch.equal(a.bytestream, b.bytestream)
+            assert torch.equal(a.bytestream_lengths, b.bytestream_lengths)
+            assert a.bytestream.untyped_storage().nbytes() == a.bytestream.numel()  # pickles without padding
+    want = torch.cat([de.decode(ser.encode(kv[:, :, s:s + chunk_tokens])) for s in range(0, T, chunk_tokens)], dim=2)
+    assert torch.equal(de.decode_many(many), want)
