@@ -393,6 +393,20 @@ def run_ours(args, spec):
         extra["e2e_reference_blob_tensors"] = measure_host(
             host_chunks, h2d, "the same call on the tensors of the reference's blob (int16 tables, int32 lengths) in pinned host memory")
         del host_chunks
+        # (3) the reference's wire format itself: pickled blobs through from_bytes, a few chunks
+        nb = min(4, len(chunks))
+        blobs = [eo.to_bytes() for eo in chunks[:nb]]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for blob in blobs:
+            de.from_bytes(blob)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        extra["from_bytes_pickle"] = {"ms_per_chunk": 1e3 * dt / nb, "blob_bytes_per_chunk": sum(map(len, blobs)) / nb,
+                                      "value": nb * kv_bytes / len(chunks) / dt / 1e9, "unit": "GB/s",
+                                      "what": "CacheGenDeserializer.from_bytes on the reference-format pickle, chunk by "
+                                              "chunk, wall clock: unpickling CUDA tensors dominates"}
+        del blobs
 
     if rank != 0:
         if world > 1:

@@ -98,3 +98,29 @@ def test_mismatched_bins_are_refused_not_misread():
     _, de_full = make_serde(256, "vllm")
     with pytest.raises(RuntimeError):
         de_full.decode(ser.encode_flat(kv))  # 17-entry tables against a 33-entry configuration's counts
+
+
+def test_corrupt_lengths_in_a_container_are_flagged_not_followed():
+    """Lengths that do not add up to the payload (or run far past it) must be reported through the
+    status word; the decode still completes and touches nothing outside the container."""
+    from cachegen_b200.serde import flat_format as ff
+    from cachegen_b200.synth import generate_kv
+    kv = generate_kv(32, 1, 128, 100, seed=4, device="cuda", dtype=torch.float16)
+    ser, de = make_serde(256, "vllm", out_dtype=torch.float16)
+    chunk = ser.encode_flat(kv)
+    good = de.decode(chunk)
+    de.check_status()
+    bad = ff.FlatChunk(chunk.blob.clone(), chunk.header)
+    ln = bad.lengths(0)
+    ln[3, 17] = 30000          # one stream claims far more bytes than the payload holds
+    ln[40, :] = 0              # a whole row of empty streams
+    out = de.decode(bad)
+    with pytest.raises(RuntimeError, match="lengths"):
+        de.check_status()
+    torch.cuda.synchronize()
+    assert out.shape == good.shape
+    # rows before the first damaged stream are untouched by the damage
+    assert torch.equal(out[:3, 0], good[:3, 0])
+    # and the decoder is usable afterwards
+    assert torch.equal(de.decode(chunk), good)
+    de.check_status()
