@@ -13,7 +13,7 @@ LIB = os.path.join(PKG, "libcachegen_b200.so")
 SOURCES = ["cg_api.cu", "cg_quant.cu", "cg_encode.cu", "cg_decode.cu"]
 HEADERS = [os.path.join(CSRC, "cg_common.cuh"), os.path.join(CSRC, "cg_coder.cuh"), os.path.join(PKG, "..", "include", "cachegen_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "--use_fast_math=false"]
+              "-Xcompiler", "-fPIC"]
 
 
 def _nvcc():
@@ -30,18 +30,18 @@ def needs_build():
 
 
 def build(force=False, verbose=False, extra_flags=(), out=None):
-    """Compiles the library; `extra_flags` (e.g. -D switches) and `out` are for experiments."""
-    global LIB
-    if out:
-        LIB, force = out, True
-    if not force and not needs_build():
-        return LIB
-    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")] + list(extra_flags)
+    """Compiles the library and returns its path.  `out` builds a second copy elsewhere (with
+    `extra_flags`, e.g. -D switches) without touching the in-tree one; CACHEGEN_B200_LIB selects it."""
+    target = out or LIB
+    if not out and not force and not needs_build():
+        return target
+    flags = NVCC_FLAGS + list(extra_flags)
     if verbose:
         flags = flags + ["-Xptxas", "-v"]
+    obj_prefix = (out + ".") if out else (CSRC + os.sep)
 
     def one(src):
-        obj = (out + "." if out else CSRC + os.sep) + src.replace(".cu", ".o")
+        obj = obj_prefix + src.replace(".cu", ".o")
         cmd = [_nvcc(), "-c", os.path.join(CSRC, src), "-o", obj] + flags
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
@@ -52,11 +52,11 @@ def build(force=False, verbose=False, extra_flags=(), out=None):
 
     with ThreadPoolExecutor(max_workers=len(SOURCES)) as ex:
         objs = list(ex.map(one, SOURCES))
-    cmd = [_nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
+    cmd = [_nvcc(), "-shared", "-o", target] + objs + ["-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    return target
 
 
 if __name__ == "__main__":
