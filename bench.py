@@ -52,6 +52,9 @@ def parse_args():
     ap.add_argument("--shard", default="requests", choices=["requests", "layers"],
                     help="N > 1: one request per GPU (weak scaling, default) or the layers of ONE request "
                          "split across the GPUs and the decoded KV gathered to GPU 0 over NCCL (strong scaling)")
+    ap.add_argument("--deliver", default="nccl", choices=["nccl", "peer"],
+                    help="--shard layers: gather the decoded slabs with NCCL after the decode (default), or let "
+                         "every decode kernel store straight into GPU 0's blob over NVLink (CUDA IPC mapping)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the baseline sample")
@@ -246,7 +249,7 @@ def run_ours(args, spec):
     from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
     from cachegen_b200.serde import CacheGenDeserializer, CacheGenSerializer
     from cachegen_b200.serde.cachegen_basics import CacheGenGPUBytestream, CacheGenGPUEncoderOutput
-    from cachegen_b200.parallel import gather_layers, max_over_ranks, partition
+    from cachegen_b200.parallel import buffer_on_root, gather_layers, max_over_ranks, partition
     from cachegen_b200.serde.cachegen_basics import CacheGenConfig
     from cachegen_b200.synth import generate_kv
 
@@ -332,13 +335,32 @@ def run_ours(args, spec):
         time.sleep(0.3)
     # ---- the headline: full decode, inputs resident in HBM
     full_out = None
+    delivery = "none"
     if by_layers:
-        if rank == 0:
-            full_out = torch.empty((L_total, 2, T, H, D), dtype=torch.float16, device=dev)
+        if args.deliver == "peer":
+            # every rank's kernel writes its layers straight into GPU 0's blob
+            shared = buffer_on_root((L_total, 2, T, H, D), torch.float16, root=0)
+            full_out = shared if rank == 0 else None
+            peer_plan = de.plan(chunks, out=shared[mine.start:mine.stop], peer_out=True)
+            delivery = "decode kernels store into GPU 0's blob over NVLink (peer mapping), no separate transfer"
 
-        def step():
-            plan.run()
-            gather_layers(out, L_total, root=0, out=full_out)
+            def step():
+                peer_plan.run()
+            # check once against the NCCL path
+            step()
+            barrier()
+            check = gather_layers(out, L_total, root=0)
+            if rank == 0:
+                assert torch.equal(check, full_out), "peer-stored KV differs from the gathered KV"
+            del check
+        else:
+            if rank == 0:
+                full_out = torch.empty((L_total, 2, T, H, D), dtype=torch.float16, device=dev)
+            delivery = "NCCL send/recv of each rank's layer slab to GPU 0, inside the step"
+
+            def step():
+                plan.run()
+                gather_layers(out, L_total, root=0, out=full_out)
     else:
         step = plan.run
     ms_step = timed(step, args.steps, max(3, args.warmup))
@@ -421,8 +443,7 @@ def run_ours(args, spec):
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong" if by_layers else "weak", "vs_baseline": None, "dtype": "u32",
         "data": "synthetic", "config": dict(describe(spec, args), shard=args.shard if world > 1 else "none",
-                                             delivery="NCCL send/recv of each rank's layer slab to GPU 0, inside the step"
-                                             if by_layers else "none"),
+                                             delivery=delivery),
         "tokens_per_s": (T if by_layers else world * T) / ms_step * 1e3,
         "bytes_per_token": per_token,
         "kv_bytes_per_token": kv_bytes / T,

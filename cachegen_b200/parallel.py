@@ -77,3 +77,52 @@ def gather_layers(local: torch.Tensor, total_layers: int, root: int = 0, out: Op
         for req in dist.batch_isend_irecv([dist.P2POp(dist.isend, local, root, group)]):
             req.wait()
     return None
+
+
+_DTYPE_STR = {torch.float16: "<f2", torch.bfloat16: "<u2", torch.uint8: "|u1", torch.float32: "<f4"}
+_ipc_mappings = []  # device pointers opened or allocated here; they live until the process exits
+
+
+class _DevicePointer:
+    """A raw device pointer dressed up for torch.as_tensor (CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _cuda_check(err, what):
+    from cuda.bindings import runtime as cudart
+    if err != cudart.cudaError_t.cudaSuccess:
+        raise RuntimeError(f"{what}: {cudart.cudaGetErrorString(err)[1].decode()}")
+
+
+def buffer_on_root(shape, dtype: torch.dtype, root: int = 0, group=None) -> torch.Tensor:
+    """Allocates one buffer of `shape` on `root`'s GPU and returns, on every rank of the box, a tensor
+    that addresses it from that rank's own GPU.
+
+    On the other ranks the memory is mapped with CUDA IPC *with their own device current*, which is
+    what makes it addressable by kernels running there (a mapping opened under the owner's device
+    index is not: kernels of another device fault on it), and peer access is enabled by the same call.
+    A decode whose output is such a tensor stores its KV straight into the consuming GPU's memory with
+    ordinary stores over NVLink, so the delivery overlaps the decode instead of following it.  Ranks
+    must synchronise (barrier) before the consumer reads.  The buffer lives until the processes exit."""
+    from cuda.bindings import runtime as cudart
+    rank = dist.get_rank(group)
+    here = torch.cuda.current_device()
+    nbytes = int(torch.Size(shape).numel()) * torch.empty((), dtype=dtype).element_size()
+    payload = [None]
+    if rank == root:
+        err, ptr = cudart.cudaMalloc(nbytes)
+        _cuda_check(err, "cudaMalloc")
+        err, handle = cudart.cudaIpcGetMemHandle(ptr)
+        _cuda_check(err, "cudaIpcGetMemHandle")
+        payload[0] = bytes(handle.reserved)
+    dist.broadcast_object_list(payload, src=root, group=group)
+    if rank != root:
+        handle = cudart.cudaIpcMemHandle_t()
+        handle.reserved = payload[0]
+        err, ptr = cudart.cudaIpcOpenMemHandle(handle, cudart.cudaIpcMemLazyEnablePeerAccess)
+        _cuda_check(err, "cudaIpcOpenMemHandle")
+    _ipc_mappings.append(int(ptr))
+    flat = torch.as_tensor(_DevicePointer(int(ptr), nbytes), device=torch.device("cuda", here))
+    return flat.view(dtype).view(shape)

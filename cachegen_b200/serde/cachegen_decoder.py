@@ -151,7 +151,8 @@ class DecodePlan:
     containers, on the GPU or in (pinned) host memory."""
 
     def __init__(self, encoder_outputs: list, bins: torch.Tensor, fmt: str,
-                 out_dtype: torch.dtype, out: torch.Tensor = None, workspace: dict = None, device=None):
+                 out_dtype: torch.dtype, out: torch.Tensor = None, workspace: dict = None, device=None,
+                 peer_out: bool = False):
         if not encoder_outputs:
             raise RuntimeError("nothing to decode")
         if fmt not in ("vllm", "huggingface"):
@@ -180,7 +181,10 @@ class DecodePlan:
         shape = (L, 2, total_T, H, D) if fmt == "vllm" else (L, 2, H, total_T, D)
         if out is None:
             out = torch.empty(shape, dtype=out_dtype, device=dev)
-        elif tuple(out.shape) != shape or out.dtype != out_dtype or out.stride(4) != 1 or out.device != dev:
+        elif (tuple(out.shape) != shape or out.dtype != out_dtype or out.stride(4) != 1 or
+              (out.device != dev and not peer_out)):
+            # peer_out: `out` is memory of another GPU of the box that this GPU can address
+            # (cachegen_b200.parallel.share_from_root); the kernel stores into it over NVLink
             raise RuntimeError("output tensor has the wrong shape, dtype, device or innermost stride")
         if fmt == "vllm":
             o_layer, o_kv, o_token, o_head = out.stride(0), out.stride(1), out.stride(2), out.stride(3)
@@ -414,10 +418,12 @@ class CacheGenDeserializer(Deserializer):
         """Status words of the pipelined path's per-group workspaces."""
         return [w["status"] for w in self._workspace.get("groups", []) if "status" in w]
 
-    def plan(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None) -> DecodePlan:
-        """The launch plan decode_many would run, for callers that decode the same chunks repeatedly."""
+    def plan(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None,
+             peer_out: bool = False) -> DecodePlan:
+        """The launch plan decode_many would run, for callers that decode the same chunks repeatedly.
+        peer_out: `out` lives on another GPU of the box (see DecodePlan)."""
         return DecodePlan(encoder_outputs, self._bins_on(_device_of(encoder_outputs[0])), self.fmt, self.out_dtype,
-                          out=out, workspace=self._workspace)
+                          out=out, workspace=self._workspace, peer_out=peer_out)
 
     def _bins_on(self, dev) -> torch.Tensor:
         if not dev.type == "cuda":
