@@ -277,7 +277,7 @@ def run_ours(args, spec):
         cfg, L, first_layer, seed = full_cfg.layer_slice(mine.start, mine.stop), len(mine), mine.start, spec["seed"]
     else:
         cfg, L, first_layer, seed = full_cfg, L_total, 0, spec["seed"] + 1000 * rank
-    ser = CacheGenSerializer(config, meta, cachegen_config=cfg)
+    ser = CacheGenSerializer(config, meta, cachegen_config=cfg, table_max_bins=full_cfg.max_bins)
     de = CacheGenDeserializer(config, meta, cachegen_config=cfg, out_dtype=torch.float16)
 
     # ---- set-up (untimed): this rank's share, encoded chunk by chunk as LMCacheEngine.store would

@@ -126,6 +126,21 @@ def encode_streams(cdf: torch.Tensor, sym: torch.Tensor, scratch_stride: int = N
     return out, lengths, offs
 
 
+def _table_bins(key_bins: torch.Tensor, value_bins: torch.Tensor, max_bins: int = None) -> int:
+    """max_bins of the chunk's tables.  The reference builds key and value tables with their own
+    maximum and concatenates them, which needs the two to be equal (enc.py:265-267).  `max_bins`
+    overrides that: a layer shard of a model must use the whole model's value so that its tables and
+    streams are the ones an unsharded encode produces."""
+    kmax, vmax = int(key_bins.max()), int(value_bins.max())
+    if max_bins is not None:
+        if max_bins < max(kmax, vmax):
+            raise RuntimeError(f"max_bins {max_bins} is below the largest bin count {max(kmax, vmax)}")
+        return int(max_bins)
+    if kmax != vmax:
+        raise RuntimeError(f"Sizes of tensors must match: key tables have {kmax + 1} entries, value tables {vmax + 1}")
+    return kmax
+
+
 class _PendingChunk:
     """One chunk whose quantise / table / coder kernels are enqueued but whose payload size is not
     yet known on the host."""
@@ -186,16 +201,14 @@ class _PendingChunk:
 
 
 def encode_many(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor, chunk_tokens: int,
-                batch: int = 16) -> list:
+                batch: int = 16, max_bins: int = None) -> list:
     """Encodes a whole KV cache [L, 2, T, H, D] (GPU, unit innermost stride) chunk by chunk, as
     LMCacheEngine.store does with one to_bytes call per chunk (LMCache/lmcache/cache_engine.py:205-255
     in the reference), but with one host synchronisation per `batch` chunks instead of one per chunk:
     all kernels of a batch are enqueued first, their payload sizes come back in one transfer, then the
     streams are gathered.  Every chunk keeps its own scratch (136 MB for a 7B-shape chunk) until then.
     Returns the chunks' CacheGenGPUEncoderOutput objects, identical to per-chunk encode_function calls."""
-    kmax, vmax = int(key_bins.max()), int(value_bins.max())
-    if kmax != vmax:
-        raise RuntimeError(f"Sizes of tensors must match: key tables have {kmax + 1} entries, value tables {vmax + 1}")
+    kmax = _table_bins(key_bins, value_bins, max_bins)
     T = kv.shape[2]
     starts = list(range(0, T, chunk_tokens))
     result = []
@@ -210,17 +223,13 @@ def encode_many(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tens
 
 
 def encode_function(kv: torch.Tensor, config: CacheGenConfig, key_bins: torch.Tensor, value_bins: torch.Tensor,
-                    chunk_size: int) -> CacheGenGPUEncoderOutput:
+                    chunk_size: int, max_bins: int = None) -> CacheGenGPUEncoderOutput:
     """Encodes one chunk of KV, [L, 2, T, H, D] on the GPU, T == chunk_size (enc.py:247-301)."""
     num_heads, head_size = kv.shape[-2:]
     L = kv.shape[0]
     if kv.shape[2] != chunk_size:
         raise RuntimeError(f"chunk_size {chunk_size} does not match the {kv.shape[2]} tokens of the blob")
-    # the reference builds K and V tables with their own max and concatenates them, which needs the
-    # two to be equal (enc.py:265-267)
-    kmax, vmax = int(key_bins.max()), int(value_bins.max())
-    if kmax != vmax:
-        raise RuntimeError(f"Sizes of tensors must match: key tables have {kmax + 1} entries, value tables {vmax + 1}")
+    kmax = _table_bins(key_bins, value_bins, max_bins)
     sym, scales, cdf = quantize_and_tables(kv, key_bins, value_bins, kmax)
     stream_bytes, lengths, offs = encode_streams(cdf, sym)
     data_chunks = []
@@ -240,15 +249,13 @@ def encode_function(kv: torch.Tensor, config: CacheGenConfig, key_bins: torch.Te
 
 
 def encode_flat(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor,
-                compact_tables: bool = True) -> flat_format.FlatChunk:
+                compact_tables: bool = True, max_bins: int = None) -> flat_format.FlatChunk:
     """Encodes one chunk of KV, [L, 2, T, H, D] on the GPU, into a CGB2 container on the GPU
     (flat_format.py): the same tables, lengths and streams as encode_function, with uint16 lengths and,
     when every non-centre histogram count fits a byte, the tables as byte counts."""
     L, _, T, H, D = kv.shape
     C = H * D
-    kmax, vmax = int(key_bins.max()), int(value_bins.max())
-    if kmax != vmax:
-        raise RuntimeError(f"Sizes of tensors must match: key tables have {kmax + 1} entries, value tables {vmax + 1}")
+    kmax = _table_bins(key_bins, value_bins, max_bins)
     sym, scales, cdf, counts, qstatus = quantize_and_tables(kv, key_bins, value_bins, kmax, with_counts=True)
     stream_bytes, lengths, offs, qbits = encode_streams(cdf, sym, extra_status=qstatus)
     use_counts = compact_tables and not (qbits & _lib.CG_S_COUNT_OVERFLOW)
@@ -276,10 +283,11 @@ class CacheGenSerializer(Serializer):
     cannot read)."""
 
     def __init__(self, config: LMCacheEngineConfig, metadata: LMCacheEngineMetadata,
-                 cachegen_config: CacheGenConfig = None, wire_format: str = "pickle"):
+                 cachegen_config: CacheGenConfig = None, wire_format: str = "pickle", table_max_bins: int = None):
         if wire_format not in ("pickle", "flat"):
             raise ValueError(f"unknown wire format {wire_format!r}")
         self.wire_format = wire_format
+        self.table_max_bins = table_max_bins  # see _table_bins: set for a layer shard of a model
         _lib.lib()  # fail at construction if the CUDA library is missing
         self.cachegen_config = cachegen_config or CacheGenConfig.from_model_name(metadata.model_name)
         self.chunk_size = config.chunk_size
@@ -298,7 +306,8 @@ class CacheGenSerializer(Serializer):
         if self.fmt == "huggingface":
             tensor = tensor.permute(0, 1, 3, 2, 4)  # a view; the kernels read it through its strides
         ntokens = tensor.shape[2]
-        return encode_function(tensor.cuda(), self.cachegen_config, self.key_bins, self.value_bins, ntokens)
+        return encode_function(tensor.cuda(), self.cachegen_config, self.key_bins, self.value_bins, ntokens,
+                               max_bins=self.table_max_bins)
 
     def encode_many(self, tensor: torch.Tensor, chunk_tokens: int = None, batch: int = 16) -> list:
         """A whole KV cache, one encoded chunk per `chunk_tokens` (default: the configured chunk size)
@@ -308,7 +317,8 @@ class CacheGenSerializer(Serializer):
         tensor = tensor.cuda()
         if tensor.stride(4) != 1:
             tensor = tensor.contiguous()
-        return encode_many(tensor, self.key_bins, self.value_bins, chunk_tokens or self.chunk_size, batch)
+        return encode_many(tensor, self.key_bins, self.value_bins, chunk_tokens or self.chunk_size, batch,
+                           max_bins=self.table_max_bins)
 
     def encode_flat(self, tensor: torch.Tensor, compact_tables: bool = True) -> flat_format.FlatChunk:
         """The chunk as a CGB2 container on the GPU."""
@@ -317,7 +327,7 @@ class CacheGenSerializer(Serializer):
         tensor = tensor.cuda()
         if tensor.stride(4) != 1:
             tensor = tensor.contiguous()
-        return encode_flat(tensor, self.key_bins, self.value_bins, compact_tables)
+        return encode_flat(tensor, self.key_bins, self.value_bins, compact_tables, max_bins=self.table_max_bins)
 
     def to_bytes(self, tensor: torch.Tensor) -> bytes:
         """KV blob ([L,2,T,H,D] for "vllm", [L,2,H,T,D] for "huggingface") -> bytes (enc.py:324-348):

@@ -237,3 +237,33 @@ def test_encode_many_equals_chunk_by_chunk_encode(chunk_tokens):
             assert a.bytestream.untyped_storage().nbytes() == a.bytestream.numel()  # pickles without padding
     want = torch.cat([de.decode(ser.encode(kv[:, :, s:s + chunk_tokens])) for s in range(0, T, chunk_tokens)], dim=2)
     assert torch.equal(de.decode_many(many), want)
+
+
+def test_layer_shard_encodes_like_the_whole_model():
+    """Layers 20..29 of the 70B configuration have 32 key bins and 16 value bins.  Encoded as a shard
+    with the whole model's table length they give exactly the whole model's tables, lengths and
+    decoded values for those layers."""
+    from cachegen_b200.serde.cachegen_basics import CacheGenConfig
+    from cachegen_b200.synth import generate_kv
+    model = "Yukang/LongAlpaca-70B-16k"
+    full = CacheGenConfig.from_model_name(model)
+    kv = generate_kv(80, 1, 128, 64, seed=3, device="cuda", dtype=torch.float16)
+    ser, de = make_serde(256, "vllm", model=model, out_dtype=torch.float16)
+    whole = ser.encode(kv)
+    want = de.decode(whole)
+    lo, hi = 20, 30
+    part_cfg = full.layer_slice(lo, hi)
+    with pytest.raises(RuntimeError, match="must match"):
+        make_serde(256, "vllm", model=model, cachegen_config=part_cfg)[0].encode(kv[lo:hi])
+    from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
+    from cachegen_b200.serde import CacheGenDeserializer, CacheGenSerializer
+    config = LMCacheEngineConfig.from_defaults(chunk_size=256)
+    meta = LMCacheEngineMetadata(model_name=model, world_size=8, worker_id=2, fmt="vllm")
+    pser = CacheGenSerializer(config, meta, cachegen_config=part_cfg, table_max_bins=full.max_bins)
+    pde = CacheGenDeserializer(config, meta, cachegen_config=part_cfg, out_dtype=torch.float16)
+    part = pser.encode(kv[lo:hi])
+    rows = list(range(lo, hi)) + list(range(80 + lo, 80 + hi))
+    assert torch.equal(part.cdf, whole.cdf[rows])
+    assert torch.equal(part.data_chunks[0].bytestream_lengths, whole.data_chunks[0].bytestream_lengths[rows])
+    assert torch.equal(pde.decode(part), want[lo:hi])
+    assert torch.equal(pde.decode(pser.encode_flat(kv[lo:hi])), want[lo:hi])
