@@ -85,9 +85,9 @@ CG_HD uint32_t cg_load_stream_word(const uint32_t *p) {
 CG_HD int equal_shifts(uint32_t low, uint32_t high) { return cg_clz((low ^ high) | 1u); }
 // ---- shared-memory access --------------------------------------------------------------------------------
 // A stream's table is the column tab[m][tid] = cdf[m] << 16 of a [rows][128] uint32 array, addressed
-// by byte address: entry m of the column starting at `col` is at col + m * kTableRowBytes.  The
-// stream's bit ring (below) is a column of the same shape.  On the device the addresses are
-// shared-memory addresses (bank = lane for every row); on the host they are offsets into a plain array.
+// by byte address: entry m of the column starting at `col` is at col + m * kTableRowBytes.  On the
+// device the addresses are shared-memory addresses (bank = lane for every row); on the host they are
+// offsets into a plain array.
 struct Smem {
 #if defined(__CUDA_ARCH__)
     __device__ __forceinline__ uint32_t ld(uint32_t addr) const {

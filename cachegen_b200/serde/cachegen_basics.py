@@ -143,13 +143,78 @@ class CacheGenGPUEncoderOutput:
 CacheGenEncoderOutput = CacheGenGPUEncoderOutput
 
 
+class _StorageRecord(pickle.Unpickler):
+    """Reads the one persistent id of a torch legacy storage stream without building the storage."""
+
+    def __init__(self, f):
+        super().__init__(f)
+        self.seen = []
+
+    def persistent_load(self, saved_id):
+        self.seen.append(saved_id)
+        return None
+
+
+def _load_storage_from_bytes(b: bytes):
+    """Replacement for torch.storage._load_from_bytes while unpickling a blob.
+
+    Pickling a tensor stores its storage as the bytes of a legacy `torch.save` stream: three small
+    pickles (magic, protocol, system info), the pickled storage whose persistent id names type,
+    location and size, the list of storage keys, then an int64 element count and the raw data.
+    torch's loader copies that data into a CPU storage and then to the GPU; here the data is viewed
+    in place inside `b` and copied once, straight to its device.  Anything unexpected falls back to
+    torch's own loader."""
+    import warnings
+    try:
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")  # TypedStorage deprecation notes; read-only buffer note
+            return _load_storage_fast(b)
+    except Exception:
+        return torch.storage._load_from_bytes(b)
+
+
+def _load_storage_fast(b: bytes):
+    f = io.BytesIO(b)
+    if pickle.load(f) != torch.serialization.MAGIC_NUMBER or pickle.load(f) != torch.serialization.PROTOCOL_VERSION:
+        raise ValueError("not a legacy stream")
+    info = pickle.load(f)
+    if not info.get("little_endian", True):
+        raise ValueError("big-endian stream")
+    rec = _StorageRecord(f)
+    rec.load()
+    keys = pickle.load(f)
+    if len(rec.seen) != 1 or len(keys) != 1:
+        raise ValueError("more than one storage")
+    typename, storage_type, key, location, numel, view = rec.seen[0]
+    if typename != "storage" or view is not None or keys[0] != key:
+        raise ValueError("storage view")
+    dtype = torch.uint8 if storage_type is torch.UntypedStorage else storage_type.dtype
+    esz = torch._utils._element_size(dtype)
+    off = f.tell()
+    count = int.from_bytes(b[off:off + 8], "little")
+    nbytes = count * esz
+    if count != numel or off + 8 + nbytes != len(b):
+        raise ValueError("size mismatch")
+    device = torch.device(location)
+    if device.type == "cuda" and not (torch.cuda.is_available() and (device.index or 0) < torch.cuda.device_count()):
+        raise ValueError("device not present")
+    if nbytes == 0:
+        raw = torch.empty(0, dtype=torch.uint8, device=device)
+    else:
+        view_cpu = torch.frombuffer(b, dtype=torch.uint8, count=nbytes, offset=off + 8)  # read-only, only read
+        raw = view_cpu.to(device) if device.type != "cpu" else view_cpu.clone()
+    return torch.storage.TypedStorage(wrap_storage=raw.untyped_storage(), dtype=dtype, _internal=True)
+
+
 class _Unpickler(pickle.Unpickler):
     """pickle loader that resolves the two wire classes to this module, whichever module path the
-    blob was written under."""
+    blob was written under, and reads tensor storages with one copy (see _load_storage_from_bytes)."""
 
     def find_class(self, module, name):
         if name in ("CacheGenGPUEncoderOutput", "CacheGenGPUBytestream") and module in (REFERENCE_MODULE, __name__):
             return globals()[name]
+        if module == "torch.storage" and name == "_load_from_bytes":
+            return _load_storage_from_bytes
         return super().find_class(module, name)
 
 

@@ -110,3 +110,33 @@ def test_wire_classes_pickle_under_the_reference_path():
     back = CacheGenEncoderOutput.from_bytes(blob)
     assert back.num_heads == 1 and back.head_size == 2 and back.data_chunks[0].ntokens == 5
     assert back["cdf"].shape == (2, 2, 3) and back.data_chunks[0]["bytestream_lengths"].sum() == 4
+
+
+def test_blob_loader_reads_storages_in_one_copy_and_like_torch():
+    """from_bytes replaces torch's storage loader with one that views the data inside the pickle; the
+    result must equal what plain pickle.load gives, views and odd dtypes included."""
+    import io
+    import pickle
+    import torch
+    from cachegen_b200.serde import cachegen_basics as B
+    base = torch.randn(6, 40, 1).to(torch.bfloat16)
+    o = B.CacheGenGPUEncoderOutput(
+        [B.CacheGenGPUBytestream(torch.arange(1000, dtype=torch.int64).to(torch.uint8), torch.ones(4, 8, dtype=torch.int32), 7),
+         B.CacheGenGPUBytestream(torch.zeros(0, dtype=torch.uint8), torch.zeros(4, 8, dtype=torch.int32), 3)],
+        torch.randint(-5, 5, (4, 8, 9), dtype=torch.int16), base[:3], base[3:, 5:15], 2, 4)
+    blob = o.to_bytes()
+    calls = []
+    orig = torch.storage._load_from_bytes
+    torch.storage._load_from_bytes = lambda b: (calls.append(1), orig(b))[1]
+    try:
+        got = B.CacheGenGPUEncoderOutput.from_bytes(blob)
+    finally:
+        torch.storage._load_from_bytes = orig
+    assert not calls  # torch's loader was never needed
+    want = pickle.load(io.BytesIO(blob))
+    for a, b in ((got.cdf, want.cdf), (got.max_tensors_key, want.max_tensors_key),
+                 (got.max_tensors_value, want.max_tensors_value),
+                 (got.data_chunks[0].bytestream, want.data_chunks[0].bytestream),
+                 (got.data_chunks[1].bytestream, want.data_chunks[1].bytestream)):
+        assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b)
+    got.cdf[0, 0, 0] = 7  # loaded tensors own writable memory
