@@ -191,7 +191,7 @@ def test_full_size_chunk_properties():
 
 
 def test_benchmark_config_one_full_round_trip_against_the_oracle(oracle):
-    """BASELINE configuration 1 at full size: Llama-7B shape (32 layers x 32 heads x 128, fp16), 1,024
+    """The first benchmark configuration at full size: Llama-7B shape (32 layers x 32 heads x 128, fp16), 1,024
     tokens, seed 0, 7B-default bins, one serializer call per 256 tokens.  Every table, length and
     stream byte and every decoded fp16 value is compared with the CPU oracle (2.7e8 symbols)."""
     from cachegen_b200.synth import WORKLOADS, generate_kv
