@@ -267,3 +267,24 @@ def test_layer_shard_encodes_like_the_whole_model():
     assert torch.equal(part.data_chunks[0].bytestream_lengths, whole.data_chunks[0].bytestream_lengths[rows])
     assert torch.equal(pde.decode(part), want[lo:hi])
     assert torch.equal(pde.decode(pser.encode_flat(kv[lo:hi])), want[lo:hi])
+
+
+@pytest.mark.parametrize("level", ["1", "2", "3"])
+def test_quant_levels_of_the_mistral_lookup_against_the_oracle(monkeypatch, oracle, level):
+    """The three QUANT_LEVEL settings (cachegen_basics.py:33-68 of the reference): level 1 mixes 16 and
+    12 bins (17-entry tables, 11-symbol rows), level 3 is 32 bins everywhere."""
+    monkeypatch.setenv("QUANT_LEVEL", level)
+    from cachegen_b200.synth import generate_kv
+    model = "mistralai/Mistral-7B-Instruct-v0.2"
+    T = 200
+    kv = generate_kv(32, 3, 40, T, seed=int(level), device="cpu", dtype=torch.float16)  # 120 channels: a ragged slab
+    ser, de = make_serde(256, "vllm", model=model, out_dtype=torch.float16)
+    eo = ser.encode(kv.cuda())
+    ref = oracle_encode(oracle, kv, ser.key_bins.cpu().numpy(), ser.value_bins.cpu().numpy(), oracle.F16)
+    assert eo.cdf.shape[2] == (17 if level == "1" else 33)
+    assert (eo.cdf.cpu().numpy() == ref["cdf"]).all()
+    assert eo.data_chunks[0].bytestream.cpu().numpy().tobytes() == ref["chunks"][0][0].tobytes()
+    want = oracle.dequantize(ref["sym"].view(np.uint8), ref["bins"], ref["max"], oracle.F16, oracle.F16)
+    assert (bits_np(kv_rows(de.decode(eo))) == want).all()
+    assert (bits_np(kv_rows(de.decode(ser.encode_flat(kv.cuda())))) == want).all()
+    de.check_status()
