@@ -429,6 +429,18 @@ def run_ours(args, spec):
                                       "what": "CacheGenDeserializer.from_bytes on the reference-format pickle, chunk by "
                                               "chunk, wall clock: unpickling CUDA tensors dominates"}
         del blobs
+        # (4) the two decoder layouts on one chunk's first sub-chunk: symbols only, same inputs and output
+        from cachegen_b200 import torchac_cuda as tcu
+        eo, dc = chunks[0], chunks[0].data_chunks[0]
+        if eo.cdf.shape[2] <= 33:
+            pref = dc.bytestream_lengths.to(torch.int64).reshape(-1).cumsum(0).reshape(dc.bytestream_lengths.shape)
+            sym = torch.empty((eo.cdf.shape[0], dc.ntokens, eo.cdf.shape[1]), dtype=torch.uint8, device=dev)
+            extra["decoder_layouts"] = {
+                "thread_per_stream_ms": timed(lambda: tcu.decode_fast_prefsum(eo.cdf, dc.bytestream, pref, sym), 10, 3),
+                "warp_per_stream_ms": timed(lambda: tcu.decode_fast_prefsum_warp(eo.cdf, dc.bytestream, pref, sym), 10, 3),
+                "what": f"decode_fast_prefsum of one {dc.ntokens}-token sub-chunk ({pref.numel()} streams) on the "
+                        "thread-per-stream kernel and on the warp-per-stream (ballot search) kernel"}
+            tcu.check_status(dev)
 
     if rank != 0:
         if world > 1:

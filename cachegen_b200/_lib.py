@@ -42,7 +42,7 @@ class DecodeJob(ctypes.Structure):
 
 EXPORTS = [
     "cg_version", "cg_status_string", "cg_last_cuda_error",
-    "cg_calculate_cdf", "cg_encode_padded", "cg_decode_padded", "cg_decode_prefsum",
+    "cg_calculate_cdf", "cg_encode_padded", "cg_decode_padded", "cg_decode_prefsum", "cg_decode_prefsum_warp",
     "cg_quantize_cdf", "cg_encode_chunk", "cg_compact_streams",
     "cg_decode_offsets", "cg_decode_dequant", "cg_decode_dequant_static",
 ]
@@ -75,6 +75,7 @@ def lib():
     L.cg_encode_padded.argtypes = [p, p, S3, i, i, i, i, p, i64, p, p, p]
     L.cg_decode_padded.argtypes = [p, p, i64, p, p, S3, i, i, i, i, p, p]
     L.cg_decode_prefsum.argtypes = [p, p, i64, p, p, S3, i, i, i, i, p, p]
+    L.cg_decode_prefsum_warp.argtypes = L.cg_decode_prefsum.argtypes
     L.cg_quantize_cdf.argtypes = [p, i, i64, i64, i64, i64, i, i, i, i, p, i, p, p, p, p, p, p, p]
     L.cg_encode_chunk.argtypes = [p, p, i, i, i, i, p, i64, p, p, p, p, p]
     L.cg_compact_streams.argtypes = [p, i64, p, p, p, i, i, i, p, p]

@@ -64,6 +64,51 @@ __global__ void __launch_bounds__(kGroup) decode_symbols_kernel(const SymDecodeP
                                 __activemask(), emit);
 }
 
+// ---- one warp per stream (kept for comparison) -------------------------------------------------------------
+// The layout usually drawn for a GPU arithmetic decoder: a warp owns one stream, lane m holds table
+// entry m in a register, a ballot over "(span * cdf[m]) >> 16 <= value - low" finds the symbol and two
+// shuffles fetch its scaled bounds.  It needs no shared memory and no search loop, but all 32 lanes
+// repeat the stream's serial range update, so it spends about 30 warp instructions per symbol where
+// the thread-per-stream kernels spend about 70 per 32 symbols.  Same results; tables of at most 33
+// entries; prefix-sum stream layout only.
+__global__ void __launch_bounds__(kGroup) decode_symbols_warp_kernel(const SymDecodeParams p, int nrows) {
+    const int lane = threadIdx.x & 31;
+    const int64_t g = (static_cast<int64_t>(blockIdx.x) * kGroup + threadIdx.x) >> 5;
+    if (g >= static_cast<int64_t>(nrows) * p.nchannels) return;
+    const int row = static_cast<int>(g / p.nchannels), c = static_cast<int>(g % p.nchannels);
+    int64_t start = g ? p.prefsum[g - 1] : 0;
+    int64_t len = p.prefsum[g] - start;
+    bool bad = false;
+    if (len < 0) { len = 0; bad = true; }
+    if (start < 0) { start = 0; len = 0; bad = true; }
+    if (start > p.nbytes) { start = p.nbytes; bad = true; }
+    if (start + len > p.nbytes) { len = p.nbytes - start; bad = true; }
+    if (len > (1 << 20)) len = 1 << 20;
+    if (bad && lane == 0 && p.status) atomicOr(p.status, CG_S_BAD_LENGTHS);
+
+    const int maxsym = p.lp - 2;
+    const uint32_t c16 = lane <= maxsym
+                             ? static_cast<uint32_t>(static_cast<uint16_t>(__ldg(p.cdf + g * p.lp + lane))) << 16
+                             : 0u;
+    BitWindow bw;
+    DecoderState st;
+    st.low = 0u;
+    st.span32 = 0u;
+    st.offset = bw.open(p.bytes + start, static_cast<uint32_t>(len));
+    uint8_t *o = p.out + row * p.o0 + c * p.o2;
+    for (int i = 0; i < p.ntokens; ++i) {
+        const uint32_t f = scale_exact(st.span32, c16);
+        const uint32_t votes = __ballot_sync(0xFFFFFFFFu, lane <= maxsym && f <= st.offset);
+        const int sym = 31 - __clz(static_cast<int>(votes | 1u));  // entry 0 is always taken
+        if (lane == 0) o[i * p.o1] = static_cast<uint8_t>(sym);
+        if (i == p.ntokens - 1) break;
+        const uint32_t flo = __shfl_sync(0xFFFFFFFFu, f, sym);
+        const uint32_t fnext = __shfl_sync(0xFFFFFFFFu, f, (sym + 1) & 31);
+        st.update(flo, sym == maxsym ? st.span32 : fnext, bw);
+        if (bw.low_water()) bw.refill();
+    }
+}
+
 // ---- fused decode + dequantise + KV-layout store --------------------------------------------------------
 struct FusedDecodeParams {
     int njobs, nlayers, nheads, head_size, nchannels, lp, nslab;
@@ -223,6 +268,23 @@ extern "C" int cg_decode_prefsum(const int16_t *cdf, const uint8_t *bytes, int64
     SymDecodeParams p{cdf, bytes, nbytes, prefsum, nullptr, 0, out, out_strides[0], out_strides[1],
                       out_strides[2], ntokens, nchannels, lp, status};
     return launch_symbols<0>(p, nrows, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cg_decode_prefsum_warp(const int16_t *cdf, const uint8_t *bytes, int64_t nbytes,
+                                      const int64_t *prefsum, uint8_t *out, const int64_t out_strides[3],
+                                      int nrows, int ntokens, int nchannels, int lp, int32_t *status,
+                                      void *stream) {
+    if (!cdf || !prefsum || !out || !out_strides || (!bytes && nbytes > 0)) return CG_E_NULL;
+    if (nbytes < 0) return CG_E_SHAPE;
+    if (int rc = check_coder_shape(nrows, ntokens, nchannels, lp)) return rc;
+    if (lp > 33) return CG_E_LP;
+    SymDecodeParams p{cdf, bytes, nbytes, prefsum, nullptr, 0, out, out_strides[0], out_strides[1],
+                      out_strides[2], ntokens, nchannels, lp, status};
+    const int64_t nstreams = static_cast<int64_t>(nrows) * nchannels;
+    const int64_t blocks = (nstreams * 32 + kGroup - 1) / kGroup;
+    if (blocks > 0x7FFFFFFF) return CG_E_SHAPE;
+    decode_symbols_warp_kernel<<<static_cast<unsigned>(blocks), kGroup, 0, static_cast<cudaStream_t>(stream)>>>(p, nrows);
+    return check_launch();
 }
 
 extern "C" int cg_decode_padded(const int16_t *cdf, const uint8_t *streams, int64_t stream_stride,

@@ -134,6 +134,16 @@ int cg_decode_prefsum(const int16_t *cdf, const uint8_t *bytes, int64_t nbytes,
                       int nrows, int ntokens, int nchannels, int lp, int32_t *status,
                       void *stream);
 
+/*
+ * The same decode as cg_decode_prefsum with one WARP per stream (lane m holds table entry m, a ballot
+ * finds the symbol).  Same results; lp <= 33.  Kept as the measured alternative to the thread-per-stream
+ * layout of every other decoder entry point: it is several times slower and nothing else uses it.
+ */
+int cg_decode_prefsum_warp(const int16_t *cdf, const uint8_t *bytes, int64_t nbytes,
+                           const int64_t *prefsum, uint8_t *out, const int64_t out_strides[3],
+                           int nrows, int ntokens, int nchannels, int lp, int32_t *status,
+                           void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * fused encode side
  * ------------------------------------------------------------------------------------------ */

@@ -175,3 +175,42 @@ def test_argument_checks_raise_like_the_reference(tc):
     pref = torch.zeros((2, 128), dtype=torch.int64, device="cuda")
     with pytest.raises(RuntimeError, match="Number of tokens"):
         tc.decode_fast_prefsum(cdf, torch.zeros(8, dtype=torch.uint8, device="cuda"), pref, out)
+
+
+@pytest.mark.parametrize("max_bins,T,C", [(32, 256, 320), (16, 77, 37), (8, 1, 128), (12, 200, 130)])
+def test_warp_per_stream_decoder_gives_the_same_symbols(oracle, tc, max_bins, T, C):
+    """The one-warp-per-stream layout (ballot search, table in registers) against the oracle and
+    against the thread-per-stream kernel, on whole and on truncated streams."""
+    rng = np.random.default_rng(max_bins * 101 + T + C)
+    NL = 2
+    sym = peaked_symbols(rng, (NL, T, C), 2 * (max_bins // 2 - 1) + 1)
+    cdf = oracle.calculate_cdf(sym, max_bins)
+    cdf_t = torch.from_numpy(cdf).cuda()
+    want_bytes, want_len = oracle.encode_chunk(cdf, sym)
+    pref = torch.from_numpy(np.cumsum(want_len.reshape(-1).astype(np.int64)).reshape(NL, C)).cuda()
+    flat = torch.from_numpy(want_bytes.copy()).cuda()
+    out = torch.full((NL, T, C), 255, dtype=torch.uint8, device="cuda")
+    tc.decode_fast_prefsum_warp(cdf_t, flat, pref, out)
+    tc.check_status()
+    assert (out.cpu().numpy() == sym.view(np.uint8)).all()
+
+    # every stream cut to half its bytes: both kernels read zeros past the end and must agree
+    half = (want_len.reshape(-1) // 2).astype(np.int64)
+    starts = np.concatenate([[0], np.cumsum(want_len.reshape(-1).astype(np.int64))[:-1]])
+    cut = np.concatenate([want_bytes[s:s + h] for s, h in zip(starts, half)] + [np.zeros(0, np.uint8)])
+    cut_t = torch.from_numpy(np.ascontiguousarray(cut)).cuda() if cut.size else torch.zeros(4, dtype=torch.uint8, device="cuda")
+    pref2 = torch.from_numpy(np.cumsum(half).reshape(NL, C)).cuda()
+    a = torch.full((NL, T, C), 255, dtype=torch.uint8, device="cuda")
+    b = torch.full((NL, T, C), 254, dtype=torch.uint8, device="cuda")
+    tc.decode_fast_prefsum(cdf_t, cut_t, pref2, a)
+    tc.decode_fast_prefsum_warp(cdf_t, cut_t, pref2, b)
+    tc.check_status()
+    assert torch.equal(a, b)
+
+
+def test_warp_per_stream_decoder_rejects_long_tables(tc):
+    cdf = torch.zeros((1, 4, 49), dtype=torch.int16, device="cuda")
+    pref = torch.zeros((1, 4), dtype=torch.int64, device="cuda")
+    out = torch.zeros((1, 8, 4), dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError):
+        tc.decode_fast_prefsum_warp(cdf, torch.zeros(8, dtype=torch.uint8, device="cuda"), pref, out)
