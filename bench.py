@@ -380,7 +380,7 @@ def run_ours(args, spec):
 
         def measure_host(host_chunks, nbytes, what):
             def e2e_step():
-                de.decode_many_host(host_chunks, out=out, groups=8)
+                de.decode_many_host(host_chunks, out=out, groups=16)
                 status_host.copy_(de.group_status_words()[-1], non_blocking=True)
             ms = timed(e2e_step, max(2, args.steps // 2), 2)
             torch.cuda.synchronize()
@@ -403,7 +403,7 @@ def run_ours(args, spec):
         del flat_plan, flat_gpu, kv
         e2e = measure_host(flat_host, sum(c.header.total for c in flat_host),
                            "CacheGenDeserializer.decode_many_host on CGB2 containers (CacheGenSerializer.encode_flat) "
-                           "held in pinned host memory; 8 groups, copies of one group overlap the decode of the previous")
+                           "held in pinned host memory; 16 groups, copies of one group overlap the decode of the previous")
         del flat_host
         # (2) the reference's blob layout (tensors of CacheGenGPUEncoderOutput), same call
         host_chunks = [CacheGenGPUEncoderOutput(

@@ -11,8 +11,8 @@ CG_MAX_TOKENS_PER_STREAM = 256
 CG_MAX_LP = 64
 CG_GROUP_CHANNELS = 128
 CG_MAX_DECODE_JOBS = 40
-CG_S_STREAM_OVERFLOW, CG_S_BAD_LENGTHS, CG_S_BAD_SYMBOL, CG_S_COUNT_OVERFLOW = 1, 2, 4, 8
-CG_TABLES_CDF, CG_TABLES_COUNTS = 0, 1
+CG_S_STREAM_OVERFLOW, CG_S_BAD_LENGTHS, CG_S_BAD_SYMBOL, CG_S_COUNT_OVERFLOW, CG_S_BAD_TABLE = 1, 2, 4, 8, 16
+CG_TABLES_CDF, CG_TABLES_COUNTS, CG_TABLES_SPARSE = 0, 1, 2
 CG_LENGTHS_I32, CG_LENGTHS_U16 = 0, 1
 CG_E_CUDA = -8
 
@@ -33,6 +33,7 @@ class DecodeJob(ctypes.Structure):
         ("out", ctypes.c_void_p),
         ("table_row_off", ctypes.c_void_p),
         ("nbytes", ctypes.c_int64),
+        ("tables_nbytes", ctypes.c_int64),
         ("ntokens", ctypes.c_int32),
         ("scale_stride", ctypes.c_int32),
         ("table_kind", ctypes.c_int32),
@@ -43,7 +44,7 @@ class DecodeJob(ctypes.Structure):
 EXPORTS = [
     "cg_version", "cg_status_string", "cg_last_cuda_error",
     "cg_calculate_cdf", "cg_encode_padded", "cg_decode_padded", "cg_decode_prefsum", "cg_decode_prefsum_warp",
-    "cg_quantize_cdf", "cg_encode_chunk", "cg_compact_streams",
+    "cg_quantize_cdf", "cg_pack_sparse_tables", "cg_encode_chunk", "cg_compact_streams",
     "cg_decode_offsets", "cg_decode_dequant", "cg_decode_dequant_static",
 ]
 CG_STATIC_OFFSET_ENTRIES = 131072
@@ -77,6 +78,7 @@ def lib():
     L.cg_decode_prefsum.argtypes = [p, p, i64, p, p, S3, i, i, i, i, p, p]
     L.cg_decode_prefsum_warp.argtypes = L.cg_decode_prefsum.argtypes
     L.cg_quantize_cdf.argtypes = [p, i, i64, i64, i64, i64, i, i, i, i, p, i, p, p, p, p, p, p, p]
+    L.cg_pack_sparse_tables.argtypes = [p, p, p, i, i, p, p, p, p, p]
     L.cg_encode_chunk.argtypes = [p, p, i, i, i, i, p, i64, p, p, p, p, p]
     L.cg_compact_streams.argtypes = [p, i64, p, p, p, i, i, i, p, p]
     L.cg_decode_offsets.argtypes = [ctypes.POINTER(DecodeJob), i, i, i, p, p, p]
@@ -116,4 +118,6 @@ def status_text(bits):
         names.append("a symbol outside the table was met while encoding")
     if bits & CG_S_COUNT_OVERFLOW:
         names.append("a histogram count does not fit the byte-count tables")
+    if bits & CG_S_BAD_TABLE:
+        names.append("sparse table offsets reach past the table set")
     return "; ".join(names) if names else "ok"

@@ -10,7 +10,7 @@ from concurrent.futures import ThreadPoolExecutor
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libcachegen_b200.so")
-SOURCES = ["cg_api.cu", "cg_quant.cu", "cg_encode.cu", "cg_decode.cu"]
+SOURCES = ["cg_api.cu", "cg_quant.cu", "cg_tables.cu", "cg_encode.cu", "cg_decode.cu"]
 HEADERS = [os.path.join(CSRC, "cg_common.cuh"), os.path.join(CSRC, "cg_coder.cuh"), os.path.join(PKG, "..", "include", "cachegen_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]

@@ -82,6 +82,39 @@ __device__ __forceinline__ void stage_table_column_from_counts(uint32_t *tab, co
     for (int i = n; i < rows; ++i) tab[i * kGroup + tid] = 0u;
 }
 
+// The same column from the sparse byte counts (CG_TABLES_SPARSE): `mask` has bit j set when stored
+// symbol j (centre skipped) has a non-zero count, and `nz` points at those counts in rising symbol
+// order (nullptr: read them all as zero).
+__device__ __forceinline__ void stage_table_column_from_sparse(uint32_t *tab, uint32_t mask, const uint8_t *nz, int cq,
+                                                               int ntokens, int lp, int rows, int tid) {
+    const int max_bins = lp - 1;
+    if (2 * cq < 32) mask &= (1u << (2 * cq)) - 1u;
+    if (!nz) mask = 0u;
+    uint32_t others = 0;
+    for (int k = __popc(mask) - 1; k >= 0; --k) others += __ldg(nz + k);
+    const uint32_t centre = static_cast<uint32_t>(ntokens) - others;
+    const uint32_t scale = 0xFFFFu - static_cast<uint32_t>(max_bins);
+    const uint32_t total = static_cast<uint32_t>(ntokens) & 0xFFFFu;
+    const bool pow2 = (total & (total - 1u)) == 0u;
+    const int sh = 31 - __clz(static_cast<int>(total | 1u));
+    const int n = lp < rows ? lp : rows;
+    uint32_t cum = 0;
+    for (int i = 0; i < n; ++i) {
+        const uint32_t prod = scale * (cum & 0xFFFFu);
+        const uint32_t nv = total ? (pow2 ? (prod >> sh) : (prod / total)) : 0u;
+        tab[i * kGroup + tid] = ((nv + static_cast<uint32_t>(i)) & 0xFFFFu) << 16;
+        uint32_t count = 0;
+        if (i == cq) {
+            count = centre;
+        } else if (i <= 2 * cq) {
+            if (mask & 1u) count = __ldg(nz++);
+            mask >>= 1;
+        }
+        cum += count;
+    }
+    for (int i = n; i < rows; ++i) tab[i * kGroup + tid] = 0u;
+}
+
 // ---- block-wide exclusive scan over kGroup (=128) ints ------------------------------------------
 // warp_sums: shared int[4].  Returns the exclusive prefix of `v` across the block.
 __device__ __forceinline__ int block_exclusive_scan_128(int v, int *warp_sums, int tid, int *total) {

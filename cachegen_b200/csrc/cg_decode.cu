@@ -157,7 +157,30 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
         lut[tid] = __fdiv_rn(__fsub_rn(static_cast<float>(tid), cq), cq);
     }
     const int rows = table_rows(p.lp, LEVELS);
-    if (active) {
+    if (job.table_kind == CG_TABLES_SPARSE) {  // the whole block: the counts are found by a scan of the masks
+        const int nrows = 2 * p.nlayers;
+        const int cq = static_cast<int>(half_range(__ldg(p.bins + row)));
+        const uint8_t *base = static_cast<const uint8_t *>(job.tables);
+        const int64_t off_masks = (static_cast<int64_t>(nrows) * p.nslab + 1) * 4 + 15 & ~int64_t{15};
+        const int64_t off_counts = off_masks + (__ldg(job.table_row_off + nrows) + 15 & ~int64_t{15});
+        uint32_t mask = 0;
+        if (active) {
+            const uint8_t *mrow = base + off_masks + __ldg(job.table_row_off + row);
+            mask = 2 * cq <= 16 ? __ldg(reinterpret_cast<const uint16_t *>(mrow) + c)
+                                : __ldg(reinterpret_cast<const uint32_t *>(mrow) + c);
+            if (2 * cq < 32) mask &= (1u << (2 * cq)) - 1u;
+        }
+        __syncthreads();  // warp_sums is free again
+        const int before = block_exclusive_scan_128(__popc(mask), warp_sums, tid, nullptr);
+        const int64_t at = off_counts +
+                           __ldg(reinterpret_cast<const uint32_t *>(base) + static_cast<int64_t>(row) * p.nslab + blockIdx.x) +
+                           before;
+        const bool fits = off_counts <= job.tables_nbytes && at + __popc(mask) <= job.tables_nbytes;
+        if (!fits && active && p.status) atomicOr(p.status, CG_S_BAD_TABLE);
+        if (active)
+            stage_table_column_from_sparse(smem, mask, fits ? base + at : nullptr, cq, job.scale_stride, p.lp,
+                                           rows + 1, tid);
+    } else if (active) {
         if (job.table_kind == CG_TABLES_COUNTS) {
             const int cq = static_cast<int>(half_range(__ldg(p.bins + row)));
             const uint8_t *cnt = static_cast<const uint8_t *>(job.tables) + __ldg(job.table_row_off + row) + c;
@@ -328,11 +351,15 @@ extern "C" int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int 
     for (int j = 0; j < njobs; ++j) {
         const cg_decode_job &jb = jobs_host[j];
         if (!jb.tables || !jb.lengths || !jb.group_off || !jb.scales_k || !jb.scales_v || !jb.out ||
-            (!jb.bytes && jb.nbytes > 0) || (jb.table_kind == CG_TABLES_COUNTS && !jb.table_row_off))
+            (!jb.bytes && jb.nbytes > 0) || (jb.table_kind != CG_TABLES_CDF && !jb.table_row_off))
             return CG_E_NULL;
-        if ((jb.table_kind != CG_TABLES_CDF && jb.table_kind != CG_TABLES_COUNTS) ||
+        if ((jb.table_kind != CG_TABLES_CDF && jb.table_kind != CG_TABLES_COUNTS && jb.table_kind != CG_TABLES_SPARSE) ||
             (jb.length_kind != CG_LENGTHS_I32 && jb.length_kind != CG_LENGTHS_U16))
             return CG_E_SHAPE;
+        if (jb.table_kind == CG_TABLES_SPARSE) {
+            if (jb.tables_nbytes < (static_cast<int64_t>(2 * nlayers) * p.nslab + 1) * 4) return CG_E_CAPACITY;
+            if (reinterpret_cast<uintptr_t>(jb.tables) & 3) return CG_E_ALIGN;
+        }
         if (jb.ntokens <= 0 || jb.nbytes < 0) return CG_E_SHAPE;
         if (jb.ntokens > CG_MAX_TOKENS_PER_STREAM) return CG_E_TOKENS;
         p.jobs[j] = jb;

@@ -99,10 +99,19 @@ class _ChunkView:
             self.mk, self.mv = sc[:h.L], sc[h.L:]
             self.tables = fc.tables()
             self.table_kind = h.table_kind
+            if (h.table_kind != flat_format.TABLES_CDF and h.bins_checksum and
+                    h.bins_checksum != flat_format.bins_checksum(bins_cpu)):
+                raise RuntimeError("the container's byte-count tables were written with other bin settings")
             if h.table_kind == flat_format.TABLES_COUNTS:
                 need = flat_format.table_row_offsets(bins_cpu, self.C)[-1]
                 if h.off_lengths - h.off_tables < need:
                     raise RuntimeError("the container's byte-count tables are smaller than the configured bins need")
+            elif h.table_kind == flat_format.TABLES_SPARSE:
+                if not flat_format.sparse_representable(bins_cpu):
+                    raise RuntimeError("sparse tables cannot describe the configured bins")
+                need = flat_format.sparse_parts(2 * h.L, self.C, flat_format.mask_row_offsets(bins_cpu, self.C)[-1])[1]
+                if h.off_lengths - h.off_tables < need:
+                    raise RuntimeError("the container's sparse tables are smaller than the configured bins need")
             self.length_kind = h.length_kind
             self.subs = [(fc.payload(j), fc.lengths(j), fc.sub_tokens(j)) for j in range(h.nsub)]
             self.table_bytes = h.off_lengths - h.off_tables
@@ -201,15 +210,18 @@ class DecodePlan:
         if status is None or status.device != dev:
             status = torch.zeros(1, dtype=torch.int32, device=dev)
             ws["status"] = status
-        row_off = None
-        if any(v.table_kind == _lib.CG_TABLES_COUNTS for v in views):
-            row_off = ws.get("table_row_off")
-            if row_off is None or row_off.device != dev or ws.get("table_row_off_c") != C:
-                row_off = torch.tensor(flat_format.table_row_offsets(bins_cpu, C), dtype=torch.int64, device=dev)
-                ws["table_row_off"], ws["table_row_off_c"] = row_off, C
+        row_offs = {}
+        for kind, name, fn in ((_lib.CG_TABLES_COUNTS, "table_row_off", flat_format.table_row_offsets),
+                               (_lib.CG_TABLES_SPARSE, "mask_row_off", flat_format.mask_row_offsets)):
+            if any(v.table_kind == kind for v in views):
+                t = ws.get(name)
+                if t is None or t.device != dev or ws.get(name + "_c") != C:
+                    t = torch.tensor(fn(bins_cpu, C), dtype=torch.int64, device=dev)
+                    ws[name], ws[name + "_c"] = t, C
+                row_offs[kind] = t
 
         esz = out.element_size()
-        self.keep = [row_off] if row_off is not None else []  # tensors that must outlive the launches
+        self.keep = list(row_offs.values())  # tensors that must outlive the launches
         jobs_all = []
         self.payload_bytes = self.table_bytes = self.length_bytes = 0
         t0 = 0
@@ -228,8 +240,9 @@ class DecodePlan:
                 job.scales_k = v.mk.data_ptr() + v.mk.element_size() * tc
                 job.scales_v = v.mv.data_ptr() + v.mv.element_size() * tc
                 job.out = out.data_ptr() + esz * (t0 + tc) * o_token
-                job.table_row_off = row_off.data_ptr() if v.table_kind == _lib.CG_TABLES_COUNTS else None
+                job.table_row_off = row_offs[v.table_kind].data_ptr() if v.table_kind in row_offs else None
                 job.nbytes = bs.numel()
+                job.tables_nbytes = v.table_bytes
                 job.ntokens = ntok
                 job.scale_stride = v.T
                 job.table_kind = v.table_kind

@@ -91,8 +91,8 @@ def encode_streams(cdf: torch.Tensor, sym: torch.Tensor, scratch_stride: int = N
 
     cdf int16 [2L, C, Lp], sym int8 [2L, T, C] contiguous.  Returns (bytes uint8 [total], lengths int32
     [nsub, 2L, C], sub_off: python list of nsub+1 byte offsets of the sub-chunks inside `bytes`).
-    Synchronises once, to size the output; `extra_status` (an int32 word) is read in the same transfer
-    and its value appended to the result.
+    Synchronises once, to size the output; `extra_status` (one or more integer words on the GPU) is read
+    in the same transfer and appended to the result (an int, or a list of ints for several words).
     """
     NL, T, C = sym.shape
     lp = cdf.shape[2]
@@ -122,7 +122,8 @@ def encode_streams(cdf: torch.Tensor, sym: torch.Tensor, scratch_stride: int = N
                                   C, _ptr(out), _stream(dev))
         _lib.check(rc, "cg_compact_streams")
     if extra_status is not None:
-        return out, lengths, offs, int(host[nsub + 2])
+        extra = [int(v) for v in host[nsub + 2:]]
+        return out, lengths, offs, (extra[0] if len(extra) == 1 else extra)
     return out, lengths, offs
 
 
@@ -248,21 +249,57 @@ def encode_function(kv: torch.Tensor, config: CacheGenConfig, key_bins: torch.Te
         num_heads=num_heads, head_size=head_size)
 
 
+def pack_sparse_tables(counts: torch.Tensor, bins: torch.Tensor, nchannels: int):
+    """Byte counts of quantize_and_tables -> the parts of the sparse table form (cg_pack_sparse_tables).
+    Returns (tables uint8 with room for every count, int32 word holding the number of counts written,
+    offset of the counts inside `tables`); the used size is that offset plus that number."""
+    dev = counts.device
+    bins_cpu = bins.cpu()
+    nrows = bins_cpu.numel()
+    count_off = torch.tensor(flat_format.table_row_offsets(bins_cpu, nchannels), dtype=torch.int64, device=dev)
+    moffs = flat_format.mask_row_offsets(bins_cpu, nchannels)
+    mask_off = torch.tensor(moffs, dtype=torch.int64, device=dev)
+    off_masks, off_counts = flat_format.sparse_parts(nrows, nchannels, moffs[-1])
+    tables = torch.zeros(off_counts + counts.numel(), dtype=torch.uint8, device=dev)
+    ngroups = nrows * ((nchannels + _lib.CG_GROUP_CHANNELS - 1) // _lib.CG_GROUP_CHANNELS)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().cg_pack_sparse_tables(_ptr(counts), _ptr(count_off), _ptr(bins), nrows, nchannels,
+                                              _ptr(tables), ctypes.c_void_p(tables.data_ptr() + off_masks),
+                                              _ptr(mask_off), ctypes.c_void_p(tables.data_ptr() + off_counts),
+                                              _stream(dev))
+    _lib.check(rc, "cg_pack_sparse_tables")
+    written = tables[4 * ngroups:4 * ngroups + 4].view(torch.int32)
+    return tables, written, off_counts
+
+
 def encode_flat(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor,
-                compact_tables: bool = True, max_bins: int = None) -> flat_format.FlatChunk:
+                compact_tables=True, max_bins: int = None) -> flat_format.FlatChunk:
     """Encodes one chunk of KV, [L, 2, T, H, D] on the GPU, into a CGB2 container on the GPU
-    (flat_format.py): the same tables, lengths and streams as encode_function, with uint16 lengths and,
-    when every non-centre histogram count fits a byte, the tables as byte counts."""
+    (flat_format.py): the same tables, lengths and streams as encode_function, with uint16 lengths and
+    the tables in the smallest form that can hold them.  compact_tables: True (sparse byte counts when
+    every non-centre histogram count fits a byte and no row has more than 32 of them, else dense byte
+    counts when the counts fit, else the int16 tables), "counts" (never sparse) or False (always int16)."""
     L, _, T, H, D = kv.shape
     C = H * D
     kmax = _table_bins(key_bins, value_bins, max_bins)
     sym, scales, cdf, counts, qstatus = quantize_and_tables(kv, key_bins, value_bins, kmax, with_counts=True)
-    stream_bytes, lengths, offs, qbits = encode_streams(cdf, sym, extra_status=qstatus)
-    use_counts = compact_tables and not (qbits & _lib.CG_S_COUNT_OVERFLOW)
-    tables = counts if use_counts else cdf.view(torch.uint8).reshape(-1)
-    header = flat_format.layout(L, H, D, T, kmax + 1, kv.dtype,
-                                flat_format.TABLES_COUNTS if use_counts else flat_format.TABLES_CDF,
-                                tables.numel(), flat_format.LENGTHS_U16, offs)
+    bins = torch.cat((key_bins, value_bins)).to(device=kv.device, dtype=torch.float32).contiguous()
+    try_sparse = compact_tables is True and flat_format.sparse_representable(bins.cpu())
+    if try_sparse:
+        sparse, written, off_counts = pack_sparse_tables(counts, bins, C)
+        extra = torch.cat((qstatus.to(torch.int64), written.to(torch.int64)))
+        stream_bytes, lengths, offs, (qbits, nwritten) = encode_streams(cdf, sym, extra_status=extra)
+    else:
+        stream_bytes, lengths, offs, qbits = encode_streams(cdf, sym, extra_status=qstatus)
+    fits = bool(compact_tables) and not (qbits & _lib.CG_S_COUNT_OVERFLOW)
+    if fits and try_sparse:
+        kind, tables = flat_format.TABLES_SPARSE, sparse[:off_counts + nwritten]
+    elif fits:
+        kind, tables = flat_format.TABLES_COUNTS, counts
+    else:
+        kind, tables = flat_format.TABLES_CDF, cdf.view(torch.uint8).reshape(-1)
+    header = flat_format.layout(L, H, D, T, kmax + 1, kv.dtype, kind, tables.numel(), flat_format.LENGTHS_U16, offs,
+                                bins_checksum=flat_format.bins_checksum(bins.cpu()))
     blob = torch.empty(header.total, dtype=torch.uint8, device=kv.device)
     head = header.pack()
     blob[:len(head)].copy_(torch.frombuffer(bytearray(head), dtype=torch.uint8), non_blocking=True)
@@ -320,7 +357,7 @@ class CacheGenSerializer(Serializer):
         return encode_many(tensor, self.key_bins, self.value_bins, chunk_tokens or self.chunk_size, batch,
                            max_bins=self.table_max_bins)
 
-    def encode_flat(self, tensor: torch.Tensor, compact_tables: bool = True) -> flat_format.FlatChunk:
+    def encode_flat(self, tensor: torch.Tensor, compact_tables=True) -> flat_format.FlatChunk:
         """The chunk as a CGB2 container on the GPU."""
         if self.fmt == "huggingface":
             tensor = tensor.permute(0, 1, 3, 2, 4)

@@ -8,7 +8,8 @@ carry the tables in a compact form:
 
   header (little-endian, 128 bytes + 8 * (nsub + 1)):
       magic "CGB2", version, L, H, D, T, Lp, nsub, scale dtype (0 fp16 / 1 bf16),
-      table kind (0 = int16 CDF tables, 1 = byte counts), length kind (0 = int32, 1 = uint16),
+      table kind (0 = int16 CDF tables, 1 = byte counts, 2 = sparse byte counts), length kind (0 = int32, 1 = uint16),
+      a checksum of the encoder's per-row bin counts (0 = not recorded),
       offsets of the four sections and the total size, then the byte offset of every sub-chunk's
       streams inside the payload section
   scales   16-bit [2L, T]: max_tensors_key rows then max_tensors_value rows
@@ -16,6 +17,9 @@ carry the tables in a compact form:
            kind 1: uint8 counts of every non-centre symbol, [row][symbol][channel] with 2*Cq_row
                    symbols per row (CG_TABLES_COUNTS in include/cachegen_b200.h); the decoder
                    rebuilds the tables from them.  Used when no such count exceeds 255.
+           kind 2: the same counts without the zeros (CG_TABLES_SPARSE): group offsets, a bit mask
+                   per (row, channel) of the symbols that occur, then the non-zero counts.  Used
+                   when kind 1 is usable and no row has more than 32 non-centre symbols.
   lengths  [nsub, 2L, C] stream lengths, uint16 (a stream is at most 520 bytes) or int32
   payload  the streams of every sub-chunk, back to back
 
@@ -23,6 +27,7 @@ Sections start on 256-byte boundaries.  Like the reference's blob, the container
 the bin settings: encoder and decoder must be configured alike.
 """
 import struct
+import zlib
 from dataclasses import dataclass
 from typing import List
 
@@ -30,10 +35,10 @@ import torch
 
 MAGIC = b"CGB2"
 VERSION = 1
-_FIXED = struct.Struct("<4sI6I3I4xQQQQQ")  # 4+4+24+12+4+40 = 88 bytes, padded to 128
+_FIXED = struct.Struct("<4sI6I3IIQQQQQ")  # 4+4+24+12+4+40 = 88 bytes, padded to 128
 HEADER_FIXED_BYTES = 128
 ALIGN = 256
-TABLES_CDF, TABLES_COUNTS = 0, 1
+TABLES_CDF, TABLES_COUNTS, TABLES_SPARSE = 0, 1, 2
 LENGTHS_I32, LENGTHS_U16 = 0, 1
 _DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1}
 _CODE_DTYPE = {0: torch.float16, 1: torch.bfloat16}
@@ -57,6 +62,35 @@ def table_row_offsets(bins_cpu: torch.Tensor, nchannels: int) -> List[int]:
     return offs
 
 
+def bins_checksum(bins_cpu: torch.Tensor) -> int:
+    """Non-zero 32-bit checksum of the per-row bin counts (key rows then value rows).  The byte-count
+    table forms can only be read with the bins they were written with; the header carries this so
+    that a decoder configured otherwise refuses the container instead of misreading it."""
+    return zlib.crc32(struct.pack(f"<{bins_cpu.numel()}H", *[int(b) for b in bins_cpu.tolist()])) or 1
+
+
+def mask_row_offsets(bins_cpu: torch.Tensor, nchannels: int) -> List[int]:
+    """Offsets of every row's masks inside the mask part of sparse tables (and the part's size): two
+    bytes per channel for rows of at most 16 non-centre symbols, else four; rows start 4-byte aligned."""
+    offs, acc = [], 0
+    for b in bins_cpu.tolist():
+        offs.append(acc)
+        acc += (nchannels * (2 if 2 * (int(b) // 2 - 1) <= 16 else 4) + 3) // 4 * 4
+    offs.append(acc)
+    return offs
+
+
+def sparse_parts(nrows: int, nchannels: int, mask_bytes: int):
+    """(offset of the masks, offset of the counts) inside sparse tables: each part starts on a
+    16-byte boundary after uint32 [nrows * ceil(C / 128) + 1] group offsets."""
+    off_masks = ((nrows * ((nchannels + 127) // 128) + 1) * 4 + 15) // 16 * 16
+    return off_masks, off_masks + (mask_bytes + 15) // 16 * 16
+
+
+def sparse_representable(bins_cpu: torch.Tensor) -> bool:
+    return all(2 * (int(b) // 2 - 1) <= 32 for b in bins_cpu.tolist())
+
+
 @dataclass
 class FlatHeader:
     L: int
@@ -68,6 +102,7 @@ class FlatHeader:
     scale_code: int
     table_kind: int
     length_kind: int
+    bins_checksum: int
     off_scales: int
     off_tables: int
     off_lengths: int
@@ -81,8 +116,8 @@ class FlatHeader:
 
     def pack(self) -> bytes:
         fixed = _FIXED.pack(MAGIC, VERSION, self.L, self.H, self.D, self.T, self.lp, self.nsub, self.scale_code,
-                            self.table_kind, self.length_kind, self.off_scales, self.off_tables, self.off_lengths,
-                            self.off_payload, self.total)
+                            self.table_kind, self.length_kind, self.bins_checksum, self.off_scales, self.off_tables,
+                            self.off_lengths, self.off_payload, self.total)
         return fixed.ljust(HEADER_FIXED_BYTES, b"\0") + struct.pack(f"<{self.nsub + 1}Q", *self.sub_off)
 
     @staticmethod
@@ -109,16 +144,16 @@ class FlatHeader:
             raise ValueError("not a CGB2 container")
         if f[1] != VERSION:
             raise ValueError(f"unsupported CGB2 version {f[1]}")
-        L, H, D, T, lp, nsub, scale_code, table_kind, length_kind = f[2:11]
+        L, H, D, T, lp, nsub, scale_code, table_kind, length_kind, bins_sum = f[2:12]
         if min(L, H, D, T, nsub) <= 0 or lp < 2 or lp > 64 or nsub != (T + 255) // 256:
             raise ValueError("corrupt CGB2 header")
-        if scale_code not in (0, 1) or table_kind not in (0, 1) or length_kind not in (0, 1):
+        if scale_code not in (0, 1) or table_kind not in (0, 1, 2) or length_kind not in (0, 1):
             raise ValueError("corrupt CGB2 header")
         end = HEADER_FIXED_BYTES + 8 * (nsub + 1)
         if len(head) < end:
             raise ValueError("truncated CGB2 header")
         sub_off = list(struct.unpack(f"<{nsub + 1}Q", head[HEADER_FIXED_BYTES:end]))
-        h = FlatHeader(L, H, D, T, lp, nsub, scale_code, table_kind, length_kind, *f[11:16], sub_off)
+        h = FlatHeader(L, H, D, T, lp, nsub, scale_code, table_kind, length_kind, bins_sum, *f[12:17], sub_off)
         C = H * D
         if h.total != total_len or not (end <= h.off_scales <= h.off_tables <= h.off_lengths <= h.off_payload <= h.total):
             raise ValueError("corrupt CGB2 section table")
@@ -132,7 +167,7 @@ class FlatHeader:
 
 
 def layout(L: int, H: int, D: int, T: int, lp: int, scale_dtype: torch.dtype, table_kind: int, table_bytes: int,
-           length_kind: int, sub_off: List[int]) -> FlatHeader:
+           length_kind: int, sub_off: List[int], bins_checksum: int = 0) -> FlatHeader:
     nsub = (T + 255) // 256
     C = H * D
     off = _up(HEADER_FIXED_BYTES + 8 * (nsub + 1))
@@ -144,8 +179,8 @@ def layout(L: int, H: int, D: int, T: int, lp: int, scale_dtype: torch.dtype, ta
     off = _up(off + nsub * 2 * L * C * (2 if length_kind == LENGTHS_U16 else 4))
     off_payload = off
     total = off + sub_off[-1]
-    return FlatHeader(L, H, D, T, lp, nsub, _DTYPE_CODE[scale_dtype], table_kind, length_kind, off_scales, off_tables,
-                      off_lengths, off_payload, total, list(sub_off))
+    return FlatHeader(L, H, D, T, lp, nsub, _DTYPE_CODE[scale_dtype], table_kind, length_kind, bins_checksum,
+                      off_scales, off_tables, off_lengths, off_payload, total, list(sub_off))
 
 
 class FlatChunk:
@@ -201,7 +236,7 @@ class FlatChunk:
         if h.table_kind == TABLES_CDF:
             n = 2 * h.L * h.H * h.D * h.lp * 2
             return self._view(h.off_tables, n, torch.int16).view(2 * h.L, h.H * h.D, h.lp)
-        return self.blob[h.off_tables:h.off_lengths]  # byte counts; the decoder knows the row offsets
+        return self.blob[h.off_tables:h.off_lengths]  # byte counts (dense or sparse); the decoder knows the row offsets
 
     def lengths(self, j: int) -> torch.Tensor:
         h = self.header

@@ -57,9 +57,20 @@ extern "C" {
  *   table_row_off[r] = nchannels * sum of 2*Cq over the rows before r.  The decoder rebuilds
  *   cdf[i] = (uint16)((0xFFFF - max_bins) * #{sym < i} / ntokens) + i from them (cal_cdf.cu:11-15,40-49):
  *   a table costs 14 or 30 bytes instead of 66.  Usable when no non-centre count exceeds 255.
+ * CG_TABLES_SPARSE: the same byte counts with the zero counts left out (cg_pack_sparse_tables writes
+ *   it).  `tables` holds three parts, each starting on a 16-byte boundary:
+ *     group_off  uint32 [nrows * G + 1], G = ceil(nchannels / 128): where each (row, 128-channel
+ *                group)'s counts start inside `counts`; the last entry is the size of `counts`
+ *     masks      per (row, channel) one bit per non-centre symbol that has a non-zero count, bit j =
+ *                stored symbol j as above; uint16 for rows with 2*Cq_r <= 16, else uint32; row r
+ *                starts table_row_off[r] bytes into the part and table_row_off[nrows] is its size
+ *     counts     the non-zero counts, one byte each: groups in (row, group) order, inside a group
+ *                channel after channel, inside a channel by rising symbol
+ *   Needs 2*Cq_r <= 32 in every row.  A typical key table costs 3 to 7 bytes.
  * Length kinds of cg_decode_job.lengths: CG_LENGTHS_I32 (the reference's int32) or CG_LENGTHS_U16. */
 #define CG_TABLES_CDF 0
 #define CG_TABLES_COUNTS 1
+#define CG_TABLES_SPARSE 2
 #define CG_LENGTHS_I32 0
 #define CG_LENGTHS_U16 1
 
@@ -80,6 +91,7 @@ extern "C" {
 #define CG_S_BAD_LENGTHS 2     /* negative length, or lengths reach past the byte array */
 #define CG_S_BAD_SYMBOL 4      /* a symbol outside [0, Lp-2] was met while encoding */
 #define CG_S_COUNT_OVERFLOW 8  /* a histogram count above 255: the byte-count tables are not usable */
+#define CG_S_BAD_TABLE 16     /* CG_TABLES_SPARSE offsets reach past the table set (read as zero counts) */
 
 const char *cg_version(void);
 const char *cg_status_string(int code);
@@ -172,6 +184,19 @@ int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, in
                     int32_t *status, void *stream);
 
 /*
+ * Byte counts (CG_TABLES_COUNTS, as cg_quantize_cdf writes them) -> CG_TABLES_SPARSE parts.  No
+ * counterpart in the reference.  counts / count_row_off [nrows]: the dense counts and their row
+ * offsets; bins: float32 [nrows] on the device.  group_off_out: uint32 [nrows * ceil(nchannels/128) + 1];
+ * masks_out with mask_row_off [nrows] (device; row r's masks start mask_row_off[r] bytes in, 4-byte
+ * aligned; 2 bytes per channel for rows with 2*Cq <= 16, else 4); counts_out: room for every count
+ * (the size of the dense counts is always enough); group_off_out's last entry tells how many were
+ * written.  The caller makes sure that no row has 2*Cq > 32.  Three launches.
+ */
+int cg_pack_sparse_tables(const uint8_t *counts, const int64_t *count_row_off, const float *bins,
+                          int nrows, int nchannels, uint32_t *group_off_out, void *masks_out,
+                          const int64_t *mask_row_off, uint8_t *counts_out, void *stream);
+
+/*
  * Replaces the sub-chunk loop of encode_function: encode_fast_new + the length bookkeeping of
  * collect_bytes for every sub-chunk of a chunk (cachegen_encoder.py:269-292,210-242).
  * sym: int8 [nrows, ntokens, nchannels] contiguous, ntokens any positive number; the chunk is cut
@@ -214,12 +239,14 @@ typedef struct cg_decode_job {
     const void *scales_v;    /* 16-bit [nlayers, scale_stride]: max_tensors_value, likewise */
     void *out;               /* 16-bit KV, element (layer 0, key, this sub-chunk's first token,
                                 head 0, d 0) of the output blob */
-    const int64_t *table_row_off; /* CG_TABLES_COUNTS only: [nrows] row offsets into `tables` */
+    const int64_t *table_row_off; /* CG_TABLES_COUNTS: [nrows] row offsets into `tables`;
+                                CG_TABLES_SPARSE: [nrows + 1] row offsets into its masks */
     int64_t nbytes;          /* size of `bytes` */
+    int64_t tables_nbytes;   /* CG_TABLES_SPARSE only: size of `tables` */
     int32_t ntokens;         /* tokens in this sub-chunk, 1..256 */
     int32_t scale_stride;    /* elements between consecutive layers in scales_k / scales_v
                                 (= the chunk's token count, over which its tables were built) */
-    int32_t table_kind;      /* CG_TABLES_CDF or CG_TABLES_COUNTS */
+    int32_t table_kind;      /* CG_TABLES_CDF, CG_TABLES_COUNTS or CG_TABLES_SPARSE */
     int32_t length_kind;     /* CG_LENGTHS_I32 or CG_LENGTHS_U16 */
 } cg_decode_job;
 

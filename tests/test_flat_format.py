@@ -67,3 +67,23 @@ def test_corrupt_headers_are_rejected(mutate):
         raw[36:40] = struct.pack("<I", 5)
     with pytest.raises(ValueError):
         ff.from_bytes(bytes(raw))
+
+
+def test_sparse_table_geometry():
+    bins = torch.tensor([32.0, 16.0, 16.0, 32.0])
+    # odd channel count: a 2-byte row of 7 channels takes 16 bytes so that the next row stays 4-byte aligned
+    assert ff.mask_row_offsets(bins, 7) == [0, 28, 44, 60, 88]
+    assert ff.mask_row_offsets(bins, 128) == [0, 512, 768, 1024, 1536]
+    off_masks, off_counts = ff.sparse_parts(4, 300, 1000)
+    assert off_masks == 64 and off_counts == 64 + 1008      # 4 rows x 3 groups + 1 offsets = 52 bytes -> 64
+    assert ff.sparse_representable(torch.tensor([34.0, 8.0])) and not ff.sparse_representable(torch.tensor([36.0]))
+    h, blob = make_blob(table_kind=ff.TABLES_SPARSE)
+    assert ff.FlatHeader.parse(blob.numpy().tobytes()).table_kind == ff.TABLES_SPARSE
+
+
+def test_bins_checksum_travels_in_the_header():
+    a, b = ff.bins_checksum(torch.tensor([32.0, 16.0])), ff.bins_checksum(torch.tensor([16.0, 8.0]))
+    assert a != b and a != 0 and b != 0
+    h = ff.layout(2, 2, 64, 10, 33, torch.float16, ff.TABLES_COUNTS, 100, ff.LENGTHS_U16, [0, 5], bins_checksum=a)
+    assert ff.FlatHeader.parse_head(h.pack(), h.total).bins_checksum == a
+    assert ff.FlatHeader.parse_head(make_blob()[0].pack(), make_blob()[0].total).bins_checksum == 0  # not recorded
