@@ -362,6 +362,7 @@ def decode_many_pipelined(encoder_outputs: List[CacheGenGPUEncoderOutput], bins:
         tg = sum(_chunk_tokens(eo) for eo in part)
         view = out[:, :, t0:t0 + tg] if fmt == "vllm" else out[:, :, :, t0:t0 + tg]
         with torch.cuda.stream(copy_stream):
+            part = _stage_flat(part, workspaces[g], dev)
             plan = DecodePlan(part, bins, fmt, out_dtype, out=view, workspace=workspaces[g], device=dev)
             ready = torch.cuda.Event()
             ready.record(copy_stream)
@@ -369,6 +370,28 @@ def decode_many_pipelined(encoder_outputs: List[CacheGenGPUEncoderOutput], bins:
         plan.run()
         t0 += tg
     return out
+
+
+def _stage_flat(part: list, ws: dict, dev) -> list:
+    """Copies a group's CGB2 containers from host memory into one device buffer that the workspace
+    keeps between calls (no allocation per call, nothing for the caching allocator to hold back while
+    the previous call's kernels still run).  Chunks of other kinds are returned as they are."""
+    if not all(isinstance(eo, flat_format.FlatChunk) and not eo.blob.is_cuda for eo in part):
+        return part
+    starts, need = [], 0
+    for eo in part:
+        starts.append(need)
+        need += (eo.blob.numel() + flat_format.ALIGN - 1) // flat_format.ALIGN * flat_format.ALIGN
+    arena = ws.get("arena")
+    if arena is None or arena.device != dev or arena.numel() < need:
+        arena = torch.empty(need, dtype=torch.uint8, device=dev)
+        ws["arena"] = arena
+    staged = []
+    for eo, a in zip(part, starts):
+        dst = arena[a:a + eo.blob.numel()]
+        dst.copy_(eo.blob, non_blocking=True)
+        staged.append(flat_format.FlatChunk(dst, eo.header))
+    return staged
 
 
 def decode_to_kv(encoder_output: CacheGenGPUEncoderOutput, bins: torch.Tensor, fmt: str, out_dtype: torch.dtype,
@@ -419,8 +442,12 @@ class CacheGenDeserializer(Deserializer):
                            out=out, workspace=self._workspace)
 
     def decode_many_host(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None,
-                         groups: int = 4) -> torch.Tensor:
-        """decode_many for chunks whose tensors sit in pinned host memory: copies and decodes overlap."""
+                         groups: int = None) -> torch.Tensor:
+        """decode_many for chunks whose tensors sit in pinned host memory: copies and decodes overlap.
+        groups: how many parts the chunks are split into (default: up to 16); the decode of a part
+        runs while the next one is copied, so the last part's decode is all that is not hidden."""
+        if groups is None:
+            groups = min(16, len(encoder_outputs))
         ws = self._workspace.setdefault("groups", [dict() for _ in range(groups)])
         if len(ws) < groups:
             ws += [dict() for _ in range(groups - len(ws))]
