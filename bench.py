@@ -400,6 +400,7 @@ def run_ours(args, spec):
             "lengths": flat_plan.length_bytes / T, "scales": flat_plan.scale_bytes / T,
             "container": sum(c.header.total for c in flat_gpu) / T}
         flat_host = [c.pin_memory() for c in flat_gpu]
+        kv_chunk0 = kv[:, :, :CHUNK_TOKENS].clone()
         del flat_plan, flat_gpu, kv
         e2e = measure_host(flat_host, sum(c.header.total for c in flat_host),
                            "CacheGenDeserializer.decode_many_host on CGB2 containers (CacheGenSerializer.encode_flat) "
@@ -441,6 +442,19 @@ def run_ours(args, spec):
                 "what": f"decode_fast_prefsum of one {dc.ntokens}-token sub-chunk ({pref.numel()} streams) on the "
                         "thread-per-stream kernel and on the warp-per-stream (ballot search) kernel"}
             tcu.check_status(dev)
+
+        # (5) one chunk at the three quality levels of the reference's adaptation runs: together and one by one
+        from cachegen_b200.serde.cachegen_basics import CacheGenConfig
+        if L == 32:
+            lv = [CacheGenConfig(10, 20, 32, 16, 16, 12, 2, 16, 12), CacheGenConfig(10, 20, 32, 32, 16, 16, 2, 32, 16),
+                  CacheGenConfig(10, 20, 32, 32, 32, 32, 2, 32, 32)]
+            sers = [CacheGenSerializer(config, meta, cachegen_config=c) for c in lv]
+            one = kv_chunk0
+            extra["encode_levels"] = {
+                "together_ms": timed(lambda: ser.encode_levels(one, lv), 5, 2),
+                "one_by_one_ms": timed(lambda: [s_.encode(one) for s_ in sers], 5, 2),
+                "what": f"one {one.shape[2]}-token chunk at QUANT_LEVEL 1, 2 and 3: CacheGenSerializer.encode_levels "
+                        "against three CacheGenSerializer.encode calls"}
 
     if rank != 0:
         if world > 1:

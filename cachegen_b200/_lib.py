@@ -44,7 +44,7 @@ class DecodeJob(ctypes.Structure):
 EXPORTS = [
     "cg_version", "cg_status_string", "cg_last_cuda_error",
     "cg_calculate_cdf", "cg_encode_padded", "cg_decode_padded", "cg_decode_prefsum", "cg_decode_prefsum_warp",
-    "cg_quantize_cdf", "cg_pack_sparse_tables", "cg_encode_chunk", "cg_compact_streams",
+    "cg_quantize_cdf", "cg_row_absmax", "cg_quantize_cdf_scaled", "cg_pack_sparse_tables", "cg_encode_chunk", "cg_compact_streams",
     "cg_decode_offsets", "cg_decode_dequant", "cg_decode_dequant_static",
 ]
 CG_STATIC_OFFSET_ENTRIES = 131072
@@ -78,6 +78,8 @@ def lib():
     L.cg_decode_prefsum.argtypes = [p, p, i64, p, p, S3, i, i, i, i, p, p]
     L.cg_decode_prefsum_warp.argtypes = L.cg_decode_prefsum.argtypes
     L.cg_quantize_cdf.argtypes = [p, i, i64, i64, i64, i64, i, i, i, i, p, i, p, p, p, p, p, p, p]
+    L.cg_row_absmax.argtypes = [p, i, i64, i64, i64, i64, i, i, i, i, p, p]
+    L.cg_quantize_cdf_scaled.argtypes = [p, i, i64, i64, i64, i64, i, i, i, i, p, i, p, p, p, p, p, p, p]
     L.cg_pack_sparse_tables.argtypes = [p, p, p, i, i, p, p, p, p, p]
     L.cg_encode_chunk.argtypes = [p, p, i, i, i, i, p, i64, p, p, p, p, p]
     L.cg_compact_streams.argtypes = [p, i64, p, p, p, i, i, i, p, p]

@@ -238,6 +238,80 @@ extern "C" int cg_calculate_cdf(const int8_t *sym, const int64_t sym_strides[3],
     return check_launch();
 }
 
+namespace {
+
+struct QuantShape {
+    KvLayout L;
+    bool vec;
+};
+
+// argument checks shared by the quantise entry points
+int quant_shape(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token, int64_t s_head,
+                int nlayers, int ntokens, int nheads, int head_size, const void *sym_out, QuantShape *q) {
+    if (nlayers <= 0 || ntokens <= 0 || nheads <= 0 || head_size <= 0 || 2 * nlayers > 65535) return CG_E_SHAPE;
+    if (ntokens >= 65536) return CG_E_HIST;
+    if (dtype != CG_F16 && dtype != CG_BF16) return CG_E_DTYPE;
+    q->L = KvLayout{s_layer, s_kv, s_token, s_head, nlayers, ntokens, nheads, head_size};
+    // the 128-bit path needs 8-channel runs that stay inside one head and 16-byte aligned rows
+    q->vec = (head_size % 8 == 0) && ((reinterpret_cast<uintptr_t>(kv) & 15) == 0) && (s_layer % 8 == 0) &&
+             (s_kv % 8 == 0) && (s_token % 8 == 0) && (s_head % 8 == 0) &&
+             ((reinterpret_cast<uintptr_t>(sym_out) & 7) == 0);
+    return CG_OK;
+}
+
+int launch_absmax(const uint16_t *x, const QuantShape &q, uint16_t *sc, cudaStream_t st) {
+    const int64_t nwarps = static_cast<int64_t>(2 * q.L.nlayers) * q.L.ntokens;
+    const unsigned ablocks = static_cast<unsigned>((nwarps * 32 + 255) / 256);
+    if (q.vec) row_absmax_kernel<8><<<ablocks, 256, 0, st>>>(x, q.L, sc);
+    else row_absmax_kernel<1><<<ablocks, 256, 0, st>>>(x, q.L, sc);
+    return check_launch();
+}
+
+int launch_quantize(const uint16_t *x, int dtype, const QuantShape &q, const float *bins, const uint16_t *sc,
+                    int max_bins, int8_t *sym_out, int16_t *cdf_out, uint8_t *counts_out,
+                    const int64_t *table_row_off, int32_t *status, cudaStream_t st) {
+    const int C = q.L.nheads * q.L.head_size;
+    const dim3 grid((C + kGroup - 1) / kGroup, 2 * q.L.nlayers);
+    const size_t smem = hist_smem_bytes(max_bins);
+#define CG_LAUNCH_Q(DT, V) \
+    quantize_cdf_kernel<DT, V><<<grid, kQuantThreads, smem, st>>>(x, q.L, bins, sc, max_bins, sym_out, cdf_out, \
+                                                                  counts_out, table_row_off, status)
+    if (dtype == CG_F16) { if (q.vec) CG_LAUNCH_Q(CG_F16, 8); else CG_LAUNCH_Q(CG_F16, 1); }
+    else { if (q.vec) CG_LAUNCH_Q(CG_BF16, 8); else CG_LAUNCH_Q(CG_BF16, 1); }
+#undef CG_LAUNCH_Q
+    return check_launch();
+}
+
+}  // namespace
+
+extern "C" int cg_row_absmax(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
+                             int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
+                             void *scales_out, void *stream) {
+    if (!kv || !scales_out) return CG_E_NULL;
+    QuantShape q;
+    // the symbol pointer only matters for the quantise pass: any 8-byte aligned value keeps the choice of load width
+    if (int rc = quant_shape(kv, dtype, s_layer, s_kv, s_token, s_head, nlayers, ntokens, nheads, head_size, nullptr, &q))
+        return rc;
+    return launch_absmax(static_cast<const uint16_t *>(kv), q, static_cast<uint16_t *>(scales_out),
+                         static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cg_quantize_cdf_scaled(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
+                                      int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
+                                      const float *bins, int max_bins, const void *scales, int8_t *sym_out,
+                                      int16_t *cdf_out, uint8_t *counts_out, const int64_t *table_row_off,
+                                      int32_t *status, void *stream) {
+    if (!kv || !bins || !sym_out || !scales || !cdf_out) return CG_E_NULL;
+    if (counts_out && !table_row_off) return CG_E_NULL;
+    if (max_bins < 1 || max_bins >= CG_MAX_LP) return CG_E_LP;
+    QuantShape q;
+    if (int rc = quant_shape(kv, dtype, s_layer, s_kv, s_token, s_head, nlayers, ntokens, nheads, head_size, sym_out, &q))
+        return rc;
+    return launch_quantize(static_cast<const uint16_t *>(kv), dtype, q, bins, static_cast<const uint16_t *>(scales),
+                           max_bins, sym_out, cdf_out, counts_out, table_row_off, status,
+                           static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
                                int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
                                const float *bins, int max_bins, int8_t *sym_out, void *scales_out,
@@ -247,29 +321,12 @@ extern "C" int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64
     if (counts_out && !table_row_off) return CG_E_NULL;
     if (nlayers <= 0 || ntokens <= 0 || nheads <= 0 || head_size <= 0 || 2 * nlayers > 65535) return CG_E_SHAPE;
     if (max_bins < 1 || max_bins >= CG_MAX_LP) return CG_E_LP;
-    if (ntokens >= 65536) return CG_E_HIST;
-    if (dtype != CG_F16 && dtype != CG_BF16) return CG_E_DTYPE;
-    const KvLayout L{s_layer, s_kv, s_token, s_head, nlayers, ntokens, nheads, head_size};
-    const int C = nheads * head_size, nrows = 2 * nlayers;
-    // the 128-bit path needs 8-channel runs that stay inside one head and 16-byte aligned rows
-    const bool vec = (head_size % 8 == 0) && ((reinterpret_cast<uintptr_t>(kv) & 15) == 0) &&
-                     (s_layer % 8 == 0) && (s_kv % 8 == 0) && (s_token % 8 == 0) && (s_head % 8 == 0) &&
-                     ((reinterpret_cast<uintptr_t>(sym_out) & 7) == 0);
+    QuantShape q;
+    if (int rc = quant_shape(kv, dtype, s_layer, s_kv, s_token, s_head, nlayers, ntokens, nheads, head_size, sym_out, &q))
+        return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint16_t *x = static_cast<const uint16_t *>(kv);
     uint16_t *sc = static_cast<uint16_t *>(scales_out);
-    const int64_t nwarps = static_cast<int64_t>(nrows) * ntokens;
-    const unsigned ablocks = static_cast<unsigned>((nwarps * 32 + 255) / 256);
-    if (vec) row_absmax_kernel<8><<<ablocks, 256, 0, st>>>(x, L, sc);
-    else row_absmax_kernel<1><<<ablocks, 256, 0, st>>>(x, L, sc);
-    if (int rc = check_launch()) return rc;
-    const dim3 grid((C + kGroup - 1) / kGroup, nrows);
-    const size_t smem = hist_smem_bytes(max_bins);
-#define CG_LAUNCH_Q(DT, V) \
-    quantize_cdf_kernel<DT, V><<<grid, kQuantThreads, smem, st>>>(x, L, bins, sc, max_bins, sym_out, cdf_out, \
-                                                                  counts_out, table_row_off, status)
-    if (dtype == CG_F16) { if (vec) CG_LAUNCH_Q(CG_F16, 8); else CG_LAUNCH_Q(CG_F16, 1); }
-    else { if (vec) CG_LAUNCH_Q(CG_BF16, 8); else CG_LAUNCH_Q(CG_BF16, 1); }
-#undef CG_LAUNCH_Q
-    return check_launch();
+    if (int rc = launch_absmax(x, q, sc, st)) return rc;
+    return launch_quantize(x, dtype, q, bins, sc, max_bins, sym_out, cdf_out, counts_out, table_row_off, status, st);
 }

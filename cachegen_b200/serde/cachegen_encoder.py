@@ -39,8 +39,22 @@ def _split_kv(tensor: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return torch.unbind(tensor.reshape(num_layers, 2, num_tokens, num_heads * head_size), dim=1)
 
 
+def row_scales(kv: torch.Tensor) -> torch.Tensor:
+    """max|x| over the channels of every (row, token): [2L, T] in kv.dtype, key rows then value rows
+    (the max1 of torch_quant_vectorized, enc.py:55).  It does not depend on the bin settings."""
+    if kv.dim() != 5 or kv.shape[1] != 2 or kv.dtype not in _DTYPES or not kv.is_cuda or kv.stride(4) != 1:
+        raise RuntimeError("expected a CUDA float16/bfloat16 KV blob [L, 2, T, H, D] with a unit innermost stride")
+    L, _, T, H, D = kv.shape
+    scales = torch.empty((2 * L, T), dtype=kv.dtype, device=kv.device)
+    with torch.cuda.device(kv.device):
+        rc = _lib.lib().cg_row_absmax(_ptr(kv), _DTYPES[kv.dtype], kv.stride(0), kv.stride(1), kv.stride(2),
+                                      kv.stride(3), L, T, H, D, _ptr(scales), _stream(kv.device))
+    _lib.check(rc, "cg_row_absmax")
+    return scales
+
+
 def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor, max_bins: int,
-                        with_counts: bool = False):
+                        with_counts: bool = False, scales: torch.Tensor = None):
     """Fused torch_quant_vectorized (K and V) + calculate_cdf (K and V) + the two torch.cat of
     encode_function (enc.py:42-59, 257-267).
 
@@ -48,7 +62,8 @@ def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: to
         the permuted view of a "huggingface" blob is read in place).
     Returns (symbols int8 [2L, T, C], scales [2L, T] in kv.dtype, tables int16 [2L, C, max_bins + 1]);
     with_counts adds (byte counts uint8 of the compact table form, int32 status word whose
-    CG_S_COUNT_OVERFLOW bit says they are unusable for this chunk).
+    CG_S_COUNT_OVERFLOW bit says they are unusable for this chunk).  `scales`: the result of row_scales
+    for this blob, when it is already known (encoding one chunk at several bin settings).
     """
     if kv.dim() != 5 or kv.shape[1] != 2:
         raise RuntimeError(f"expected a KV blob of shape [L, 2, T, H, D], got {tuple(kv.shape)}")
@@ -65,7 +80,12 @@ def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: to
     if bins.numel() != 2 * L:
         raise RuntimeError(f"bins describe {bins.numel() // 2} layers, the KV blob has {L}")
     sym = torch.empty((2 * L, T, C), dtype=torch.int8, device=dev)
-    scales = torch.empty((2 * L, T), dtype=kv.dtype, device=dev)
+    given = scales is not None
+    if given and (tuple(scales.shape) != (2 * L, T) or scales.dtype != kv.dtype or scales.device != dev or
+                  not scales.is_contiguous()):
+        raise RuntimeError("scales must be a contiguous [2L, T] tensor of the blob's dtype on its device")
+    if not given:
+        scales = torch.empty((2 * L, T), dtype=kv.dtype, device=dev)
     cdf = torch.empty((2 * L, C, max_bins + 1), dtype=torch.int16, device=dev)
     counts = row_off = status = None
     if with_counts:
@@ -74,12 +94,15 @@ def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: to
         counts = torch.empty(offs[-1], dtype=torch.uint8, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
     null = ctypes.c_void_p(None)
+    tail = (_ptr(cdf), _ptr(counts) if with_counts else null, _ptr(row_off) if with_counts else null,
+            _ptr(status) if with_counts else null, _stream(dev))
+    head = (_ptr(kv), _DTYPES[kv.dtype], kv.stride(0), kv.stride(1), kv.stride(2), kv.stride(3), L, T, H, D,
+            _ptr(bins), int(max_bins))
     with torch.cuda.device(dev):
-        rc = _lib.lib().cg_quantize_cdf(_ptr(kv), _DTYPES[kv.dtype], kv.stride(0), kv.stride(1), kv.stride(2),
-                                        kv.stride(3), L, T, H, D, _ptr(bins), int(max_bins), _ptr(sym),
-                                        _ptr(scales), _ptr(cdf), _ptr(counts) if with_counts else null,
-                                        _ptr(row_off) if with_counts else null, _ptr(status) if with_counts else null,
-                                        _stream(dev))
+        if given:
+            rc = _lib.lib().cg_quantize_cdf_scaled(*head, _ptr(scales), _ptr(sym), *tail)
+        else:
+            rc = _lib.lib().cg_quantize_cdf(*head, _ptr(sym), _ptr(scales), *tail)
     _lib.check(rc, "cg_quantize_cdf")
     if with_counts:
         return sym, scales, cdf, counts, status
@@ -146,10 +169,10 @@ class _PendingChunk:
     """One chunk whose quantise / table / coder kernels are enqueued but whose payload size is not
     yet known on the host."""
 
-    def __init__(self, kv, key_bins, value_bins, max_bins):
+    def __init__(self, kv, key_bins, value_bins, max_bins, scales=None):
         self.L, _, self.T, self.H, self.D = kv.shape
         self.dtype = kv.dtype
-        self.sym, self.scales, self.cdf = quantize_and_tables(kv, key_bins, value_bins, max_bins)
+        self.sym, self.scales, self.cdf = quantize_and_tables(kv, key_bins, value_bins, max_bins, scales=scales)
         NL, T, C = self.sym.shape
         dev = self.sym.device
         self.nsub = (T + CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK - 1) // CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK
@@ -221,6 +244,25 @@ def encode_many(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tens
             result.append(p.finish(host[pos:pos + p.nsub + 2]))
             pos += p.nsub + 2
     return result
+
+
+def encode_levels(kv: torch.Tensor, levels: list) -> list:
+    """One chunk of KV, [L, 2, T, H, D] on the GPU, encoded at several bin settings: `levels` is a list
+    of (key_bins, value_bins) pairs, the result one CacheGenGPUEncoderOutput per pair, each identical
+    to what encode_function gives with those bins.  This is what the reference's adaptation scripts
+    store per chunk (one blob per QUANT_LEVEL, run_adaptation.py:61-72) so that config_selection can
+    pick a level per chunk (src/utils.py:294-314).  The levels share the max|x| pass and one host
+    synchronisation; the coder runs once per level, and it is what an encode spends most time in."""
+    if kv.stride(4) != 1:
+        kv = kv.contiguous()
+    scales = row_scales(kv)
+    pending = [_PendingChunk(kv, kb, vb, _table_bins(kb, vb), scales=scales) for kb, vb in levels]
+    host = torch.cat([p.tail for p in pending]).cpu()  # the one synchronisation
+    out, pos = [], 0
+    for p in pending:
+        out.append(p.finish(host[pos:pos + p.nsub + 2]))
+        pos += p.nsub + 2
+    return out
 
 
 def encode_function(kv: torch.Tensor, config: CacheGenConfig, key_bins: torch.Tensor, value_bins: torch.Tensor,
@@ -356,6 +398,16 @@ class CacheGenSerializer(Serializer):
             tensor = tensor.contiguous()
         return encode_many(tensor, self.key_bins, self.value_bins, chunk_tokens or self.chunk_size, batch,
                            max_bins=self.table_max_bins)
+
+    def encode_levels(self, tensor: torch.Tensor, cachegen_configs: list) -> list:
+        """The chunk encoded with each of `cachegen_configs` (CacheGenConfig objects, e.g. the three
+        QUANT_LEVEL settings) in one go: one CacheGenGPUEncoderOutput per configuration, equal to what
+        a serializer built with that configuration returns from `encode`."""
+        if self.fmt == "huggingface":
+            tensor = tensor.permute(0, 1, 3, 2, 4)
+        tensor = tensor.cuda()
+        return encode_levels(tensor, [(CGBasics.make_key_bins(c, tensor.device), CGBasics.make_value_bins(c, tensor.device))
+                                      for c in cachegen_configs])
 
     def encode_flat(self, tensor: torch.Tensor, compact_tables=True) -> flat_format.FlatChunk:
         """The chunk as a CGB2 container on the GPU."""

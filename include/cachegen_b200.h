@@ -184,6 +184,21 @@ int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, in
                     int32_t *status, void *stream);
 
 /*
+ * The two halves of cg_quantize_cdf on their own, for encoding one chunk at several bin settings
+ * (the quality levels of cachegen_basics.py:33-68, which src/utils.py:294-314 chooses among per chunk):
+ * the scales do not depend on the bins, so cg_row_absmax runs once and cg_quantize_cdf_scaled once per
+ * level with `scales` as an input.  Arguments as for cg_quantize_cdf.
+ */
+int cg_row_absmax(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
+                  int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
+                  void *scales_out, void *stream);
+int cg_quantize_cdf_scaled(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
+                           int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
+                           const float *bins, int max_bins, const void *scales, int8_t *sym_out,
+                           int16_t *cdf_out, uint8_t *counts_out, const int64_t *table_row_off,
+                           int32_t *status, void *stream);
+
+/*
  * Byte counts (CG_TABLES_COUNTS, as cg_quantize_cdf writes them) -> CG_TABLES_SPARSE parts.  No
  * counterpart in the reference.  counts / count_row_off [nrows]: the dense counts and their row
  * offsets; bins: float32 [nrows] on the device.  group_off_out: uint32 [nrows * ceil(nchannels/128) + 1];

@@ -288,3 +288,36 @@ def test_quant_levels_of_the_mistral_lookup_against_the_oracle(monkeypatch, orac
     assert (bits_np(kv_rows(de.decode(eo))) == want).all()
     assert (bits_np(kv_rows(de.decode(ser.encode_flat(kv.cuda())))) == want).all()
     de.check_status()
+
+
+@pytest.mark.parametrize("fmt,T", [("vllm", 256), ("huggingface", 300)])
+def test_levels_encoded_together_equal_levels_encoded_alone(monkeypatch, fmt, T):
+    """encode_levels (shared max|x| pass, one host synchronisation) returns, per QUANT_LEVEL, the blob
+    a serializer configured for that level alone produces, and the sizes drive the level choice."""
+    from cachegen_b200.serde.adaptation import config_selection, level_sizes
+    from cachegen_b200.serde.cachegen_basics import CacheGenConfig
+    from cachegen_b200.synth import generate_kv
+    model = "mistralai/Mistral-7B-Instruct-v0.2"
+    kv = generate_kv(32, 2, 64, T, seed=T, device="cuda", dtype=torch.bfloat16)
+    blob = kv if fmt == "vllm" else kv.permute(0, 1, 3, 2, 4).contiguous()
+    configs, alone = [], []
+    for level in ("1", "2", "3"):
+        monkeypatch.setenv("QUANT_LEVEL", level)
+        configs.append(CacheGenConfig.from_model_name(model))
+        ser, de = make_serde(512, fmt, model=model)
+        alone.append(ser.encode(blob))
+    together = ser.encode_levels(blob, configs)
+    assert len(together) == 3
+    for a, b in zip(alone, together):
+        assert torch.equal(a.cdf, b.cdf)
+        assert torch.equal(a.max_tensors_key, b.max_tensors_key) and torch.equal(a.max_tensors_value, b.max_tensors_value)
+        assert len(a.data_chunks) == len(b.data_chunks)
+        for x, y in zip(a.data_chunks, b.data_chunks):
+            assert x.ntokens == y.ntokens and torch.equal(x.bytestream, y.bytestream)
+            assert torch.equal(x.bytestream_lengths, y.bytestream_lengths)
+    sizes = level_sizes(together)
+    assert sizes[1] < sizes[2] < sizes[3]
+    # a link that carries level 2 but not level 3 within the chunk's share of the target
+    bw = sizes[2] * 8 / 1e9 / 0.09
+    ttft, cfg = config_selection([bw], chunk_delay=1.0, slo=0.1, sizes=[sizes])
+    assert cfg == [2] and abs(ttft - 0.09) < 1e-9
