@@ -321,3 +321,35 @@ def test_levels_encoded_together_equal_levels_encoded_alone(monkeypatch, fmt, T)
     bw = sizes[2] * 8 / 1e9 / 0.09
     ttft, cfg = config_selection([bw], chunk_delay=1.0, slo=0.1, sizes=[sizes])
     assert cfg == [2] and abs(ttft - 0.09) < 1e-9
+
+
+def test_gqa_long_context_shape_decodes_streams_the_oracle_encoded(oracle):
+    """The third benchmark configuration's shape (32 layers x 8 KV heads x 128, key rho 0.95, seed 2) at
+    three chunks: decode only, from blobs whose tables and streams come from the CPU oracle, not from
+    this package's encoder; every decoded value against the oracle's dequantisation."""
+    from cachegen_b200.serde.cachegen_basics import CacheGenGPUBytestream, CacheGenGPUEncoderOutput
+    from cachegen_b200.synth import WORKLOADS, generate_kv
+    spec = WORKLOADS["mistral7b-gqa-32k"]
+    L, H, D, T = spec["num_layers"], spec["num_heads"], spec["head_size"], 768
+    kv = generate_kv(L, H, D, T, spec["seed"], key_rho=spec["key_rho"], device="cpu", dtype=torch.float16)
+    ser, de = make_serde(256, "vllm", model=spec["model_name"], out_dtype=torch.float16)
+    kb, vb = ser.key_bins.cpu().numpy(), ser.value_bins.cpu().numpy()
+    blobs, wants = [], []
+    for s in range(0, T, 256):
+        part = kv[:, :, s:s + 256].contiguous()
+        ref = oracle_encode(oracle, part, kb, vb, oracle.F16)
+        stream_bytes, lengths = ref["chunks"][0]
+        mx = torch.from_numpy(ref["max"].reshape(2 * L, 256).view(np.float16).copy())
+        blobs.append(CacheGenGPUEncoderOutput(
+            [CacheGenGPUBytestream(torch.from_numpy(stream_bytes.copy()).cuda(),
+                                   torch.from_numpy(lengths.astype(np.int32).reshape(2 * L, H * D)).cuda(), 256)],
+            torch.from_numpy(ref["cdf"].copy()).cuda(), mx[:L].unsqueeze(-1).cuda(), mx[L:].unsqueeze(-1).cuda(), H, D))
+        wants.append(oracle.dequantize(ref["sym"].view(np.uint8), ref["bins"], ref["max"], oracle.F16, oracle.F16))
+    out = de.decode_many(blobs)
+    de.check_status()
+    assert tuple(out.shape) == (L, 2, T, H, D)
+    for i, want in enumerate(wants):
+        assert (bits_np(kv_rows(out[:, :, i * 256:(i + 1) * 256])) == want).all()
+    # the same blobs through the pickle, one by one
+    got = de.from_bytes(blobs[1].to_bytes())
+    assert (bits_np(kv_rows(got)) == wants[1]).all()
