@@ -2,11 +2,15 @@
 
 `to_bytes` keeps the reference's contract -- KV blob tensor in, pickled CacheGenGPUEncoderOutput out,
 byte-identical to what the reference produces from the same input -- with the reference's chain of
-torch ops and per-sub-chunk launches replaced by four C-ABI calls:
+torch ops and per-sub-chunk launches replaced by three C-ABI calls:
 
     cg_quantize_cdf      split K/V + quantise + histogram + tables      (enc.py:257-267)
     cg_encode_chunk      every sub-chunk's streams + offsets            (enc.py:269-292, 225-236)
     cg_compact_streams   gather of the streams                          (enc.py:210-222)
+
+Beside it: encode_many (a whole cache, one host synchronisation per batch of chunks), encode_levels
+(one chunk at several bin settings: cg_row_absmax + cg_quantize_cdf_scaled per level) and encode_flat
+(the CGB2 container of flat_format.py, tables packed by cg_pack_sparse_tables).
 
 (enc.py = cachegen_encoder.py of the reference.)
 """
@@ -54,7 +58,7 @@ def row_scales(kv: torch.Tensor) -> torch.Tensor:
 
 
 def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor, max_bins: int,
-                        with_counts: bool = False, scales: torch.Tensor = None):
+                        with_counts: bool = False, scales: torch.Tensor = None, bins_cpu: torch.Tensor = None):
     """Fused torch_quant_vectorized (K and V) + calculate_cdf (K and V) + the two torch.cat of
     encode_function (enc.py:42-59, 257-267).
 
@@ -63,7 +67,8 @@ def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: to
     Returns (symbols int8 [2L, T, C], scales [2L, T] in kv.dtype, tables int16 [2L, C, max_bins + 1]);
     with_counts adds (byte counts uint8 of the compact table form, int32 status word whose
     CG_S_COUNT_OVERFLOW bit says they are unusable for this chunk).  `scales`: the result of row_scales
-    for this blob, when it is already known (encoding one chunk at several bin settings).
+    for this blob, when it is already known (encoding one chunk at several bin settings).  `bins_cpu`:
+    a host copy of the concatenated bins, to save the transfer.
     """
     if kv.dim() != 5 or kv.shape[1] != 2:
         raise RuntimeError(f"expected a KV blob of shape [L, 2, T, H, D], got {tuple(kv.shape)}")
@@ -89,7 +94,7 @@ def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: to
     cdf = torch.empty((2 * L, C, max_bins + 1), dtype=torch.int16, device=dev)
     counts = row_off = status = None
     if with_counts:
-        offs = flat_format.table_row_offsets(bins.cpu(), C)
+        offs = flat_format.table_row_offsets(bins.cpu() if bins_cpu is None else bins_cpu, C)
         row_off = torch.tensor(offs, dtype=torch.int64, device=dev)
         counts = torch.empty(offs[-1], dtype=torch.uint8, device=dev)
         status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -291,12 +296,12 @@ def encode_function(kv: torch.Tensor, config: CacheGenConfig, key_bins: torch.Te
         num_heads=num_heads, head_size=head_size)
 
 
-def pack_sparse_tables(counts: torch.Tensor, bins: torch.Tensor, nchannels: int):
+def pack_sparse_tables(counts: torch.Tensor, bins: torch.Tensor, nchannels: int, bins_cpu: torch.Tensor = None):
     """Byte counts of quantize_and_tables -> the parts of the sparse table form (cg_pack_sparse_tables).
     Returns (tables uint8 with room for every count, int32 word holding the number of counts written,
     offset of the counts inside `tables`); the used size is that offset plus that number."""
     dev = counts.device
-    bins_cpu = bins.cpu()
+    bins_cpu = bins.cpu() if bins_cpu is None else bins_cpu
     nrows = bins_cpu.numel()
     count_off = torch.tensor(flat_format.table_row_offsets(bins_cpu, nchannels), dtype=torch.int64, device=dev)
     moffs = flat_format.mask_row_offsets(bins_cpu, nchannels)
@@ -324,11 +329,13 @@ def encode_flat(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tens
     L, _, T, H, D = kv.shape
     C = H * D
     kmax = _table_bins(key_bins, value_bins, max_bins)
-    sym, scales, cdf, counts, qstatus = quantize_and_tables(kv, key_bins, value_bins, kmax, with_counts=True)
     bins = torch.cat((key_bins, value_bins)).to(device=kv.device, dtype=torch.float32).contiguous()
-    try_sparse = compact_tables is True and flat_format.sparse_representable(bins.cpu())
+    bins_cpu = bins.cpu()
+    sym, scales, cdf, counts, qstatus = quantize_and_tables(kv, key_bins, value_bins, kmax, with_counts=True,
+                                                            bins_cpu=bins_cpu)
+    try_sparse = compact_tables is True and flat_format.sparse_representable(bins_cpu)
     if try_sparse:
-        sparse, written, off_counts = pack_sparse_tables(counts, bins, C)
+        sparse, written, off_counts = pack_sparse_tables(counts, bins, C, bins_cpu)
         extra = torch.cat((qstatus.to(torch.int64), written.to(torch.int64)))
         stream_bytes, lengths, offs, (qbits, nwritten) = encode_streams(cdf, sym, extra_status=extra)
     else:
@@ -341,7 +348,7 @@ def encode_flat(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tens
     else:
         kind, tables = flat_format.TABLES_CDF, cdf.view(torch.uint8).reshape(-1)
     header = flat_format.layout(L, H, D, T, kmax + 1, kv.dtype, kind, tables.numel(), flat_format.LENGTHS_U16, offs,
-                                bins_checksum=flat_format.bins_checksum(bins.cpu()))
+                                bins_checksum=flat_format.bins_checksum(bins_cpu))
     blob = torch.empty(header.total, dtype=torch.uint8, device=kv.device)
     head = header.pack()
     blob[:len(head)].copy_(torch.frombuffer(bytearray(head), dtype=torch.uint8), non_blocking=True)

@@ -138,11 +138,7 @@ def decode_fast_new(cdf: torch.Tensor, bytestreams: torch.Tensor, lengths: torch
     _lib.check(rc, "decode_fast_new")
 
 
-def decode_fast_prefsum(cdf: torch.Tensor, bytestreams: torch.Tensor, lengths_prefsum: torch.Tensor,
-                        output: torch.Tensor) -> None:
-    """Decodes back-to-back streams located by an inclusive int64 prefix sum of their lengths into
-    uint8 symbols [nlayers, ntokens, nchannels], strided output allowed
-    (torchac_kernel_dec_new.cu:403-479)."""
+def _decode_prefsum(entry: str, cdf, bytestreams, lengths_prefsum, output) -> None:
     _check(cdf.is_cuda, "CDF should be on GPU")
     _check(bytestreams.is_cuda, "Bytestreams should be on GPU")
     _check(lengths_prefsum.is_cuda, "Lengths should be on GPU")
@@ -161,24 +157,23 @@ def decode_fast_prefsum(cdf: torch.Tensor, bytestreams: torch.Tensor, lengths_pr
     _check(lengths_prefsum.dtype == torch.int64 and cdf.dtype == torch.int16 and bytestreams.dim() == 1,
            "expected int16 cdf, 1-D bytestreams and int64 prefix sums")
     status = _status_word(cdf.device)
-    fn = _lib.lib().cg_decode_prefsum_warp if _warp_per_stream else _lib.lib().cg_decode_prefsum
     with torch.cuda.device(cdf.device):
-        rc = fn(_ptr(cdf), _ptr(bytestreams), bytestreams.numel(), _ptr(lengths_prefsum),
-                _ptr(output), _lib.strides3(output), nlayers, ntokens, nchannels, lp,
-                _ptr(status), _stream(cdf))
+        rc = getattr(_lib.lib(), entry)(_ptr(cdf), _ptr(bytestreams), bytestreams.numel(), _ptr(lengths_prefsum),
+                                        _ptr(output), _lib.strides3(output), nlayers, ntokens, nchannels, lp,
+                                        _ptr(status), _stream(cdf))
     _lib.check(rc, "decode_fast_prefsum")
 
 
-_warp_per_stream = False
+def decode_fast_prefsum(cdf: torch.Tensor, bytestreams: torch.Tensor, lengths_prefsum: torch.Tensor,
+                        output: torch.Tensor) -> None:
+    """Decodes back-to-back streams located by an inclusive int64 prefix sum of their lengths into
+    uint8 symbols [nlayers, ntokens, nchannels], strided output allowed
+    (torchac_kernel_dec_new.cu:403-479)."""
+    _decode_prefsum("cg_decode_prefsum", cdf, bytestreams, lengths_prefsum, output)
 
 
 def decode_fast_prefsum_warp(cdf: torch.Tensor, bytestreams: torch.Tensor, lengths_prefsum: torch.Tensor,
                              output: torch.Tensor) -> None:
     """decode_fast_prefsum on the one-warp-per-stream kernel (tables of at most 33 entries): the same
     symbols, several times slower; exists so that the two layouts can be compared on the same input."""
-    global _warp_per_stream
-    _warp_per_stream = True
-    try:
-        decode_fast_prefsum(cdf, bytestreams, lengths_prefsum, output)
-    finally:
-        _warp_per_stream = False
+    _decode_prefsum("cg_decode_prefsum_warp", cdf, bytestreams, lengths_prefsum, output)
