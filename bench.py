@@ -428,7 +428,7 @@ def run_ours(args, spec):
         extra["from_bytes_pickle"] = {"ms_per_chunk": 1e3 * dt / nb, "blob_bytes_per_chunk": sum(map(len, blobs)) / nb,
                                       "value": nb * kv_bytes / len(chunks) / dt / 1e9, "unit": "GB/s",
                                       "what": "CacheGenDeserializer.from_bytes on the reference-format pickle, chunk by "
-                                              "chunk, wall clock: unpickling CUDA tensors dominates"}
+                                              "chunk, wall clock: the load of the blob (30 MB per chunk through pinned staging) dominates"}
         del blobs
         # (4) the two decoder layouts on one chunk's first sub-chunk: symbols only, same inputs and output
         from cachegen_b200 import torchac_cuda as tcu

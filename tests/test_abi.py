@@ -140,3 +140,36 @@ def test_blob_loader_reads_storages_in_one_copy_and_like_torch():
                  (got.data_chunks[1].bytestream, want.data_chunks[1].bytestream)):
         assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b)
     got.cdf[0, 0, 0] = 7  # loaded tensors own writable memory
+
+
+def test_blob_loader_views_large_storages_instead_of_copying_them():
+    """Byte strings of 64 KB and more (the pickled storages of tables and streams) must reach the
+    storage loader as views of the blob, and a blob the view reader cannot parse must still load."""
+    import torch
+    from cachegen_b200.serde import cachegen_basics as B
+    big = torch.arange(300_000, dtype=torch.int32).to(torch.uint8)
+    o = B.CacheGenGPUEncoderOutput([B.CacheGenGPUBytestream(big, torch.ones(4, 8, dtype=torch.int32), 7)],
+                                   torch.arange(4 * 8 * 33, dtype=torch.int16).reshape(4, 8, 33),
+                                   torch.ones(2, 7, 1, dtype=torch.float16), torch.ones(2, 7, 1, dtype=torch.float16), 2, 4)
+    blob = o.to_bytes()
+    kinds = []
+    orig = B._load_storage_fast
+    B._load_storage_fast = lambda b: (kinds.append((type(b).__name__, len(b))), orig(b))[1]
+    try:
+        got = B.CacheGenGPUEncoderOutput.from_bytes(blob)
+    finally:
+        B._load_storage_fast = orig
+    assert torch.equal(got.data_chunks[0].bytestream, big) and torch.equal(got.cdf, o.cdf)
+    assert any(k == "memoryview" and n > 300_000 for k, n in kinds)
+    # the reader: small reads are bytes (the unpickler indexes them), large ones views, lines end at \n
+    r = B._ViewReader(b"ab\ncd" + bytes(70_000))
+    assert r.readline() == b"ab\n" and r.read(2) == b"cd" and isinstance(r.read(65_536), memoryview)
+    assert len(r.read()) == 70_000 - 65_536 and r.read(5) == b""
+    # fallback: a failure inside the view unpickler leaves the standard one to load the blob
+    orig_cls = B._ViewUnpickler
+    B._ViewUnpickler = lambda data: (_ for _ in ()).throw(RuntimeError("no"))
+    try:
+        again = B.load_blob(blob)
+    finally:
+        B._ViewUnpickler = orig_cls
+    assert torch.equal(again.data_chunks[0].bytestream, big)
