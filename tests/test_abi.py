@@ -173,3 +173,36 @@ def test_blob_loader_views_large_storages_instead_of_copying_them():
     finally:
         B._ViewUnpickler = orig_cls
     assert torch.equal(again.data_chunks[0].bytestream, big)
+
+
+def test_blob_writer_gives_the_bytes_of_pickle_dump():
+    """to_bytes builds each tensor's legacy torch.save stream itself (one copy through pinned memory on
+    the GPU); the result must be pickle.dump's, byte for byte, also for tensors it leaves to torch
+    (views that do not own their storage) and for empty ones."""
+    import io
+    import pickle
+    import warnings
+    import torch
+    from cachegen_b200.serde import cachegen_basics as B
+    warnings.simplefilter("ignore")
+    base = torch.randn(6, 40, 1).to(torch.bfloat16)
+    o = B.CacheGenGPUEncoderOutput(
+        [B.CacheGenGPUBytestream(torch.arange(400_000, dtype=torch.int64).to(torch.uint8), torch.ones(4, 8, dtype=torch.int32), 7),
+         B.CacheGenGPUBytestream(torch.zeros(0, dtype=torch.uint8), torch.zeros(4, 8, dtype=torch.int32), 3)],
+        torch.randint(-5, 5, (40, 80, 33), dtype=torch.int16), base[:3].clone().to(torch.float16), base[3:, 5:15], 2, 4)
+    f = io.BytesIO()
+    pickle.dump(o, f)
+    made = []
+    orig = B._legacy_stream_head
+    B._legacy_stream_head = lambda *a: (made.append(a[0]), orig(*a))[1]
+    try:
+        assert o.to_bytes() == f.getvalue()
+    finally:
+        B._legacy_stream_head = orig
+    # every tensor but the view took the fast path
+    assert sorted(map(str, made)) == sorted(map(str, [torch.uint8, torch.int32, torch.uint8, torch.int32, torch.int16, torch.float16]))
+    for dt in (torch.uint8, torch.int16, torch.int32, torch.float16, torch.bfloat16):
+        t = torch.arange(1000).to(dt)
+        want = t._typed_storage().__reduce__()[1][0]   # torch's own stream of this storage
+        head = B._legacy_stream_head(dt, str(t.untyped_storage()._cdata), "cpu", t.numel())
+        assert head + bytes(memoryview(t.view(torch.uint8).numpy())) == want

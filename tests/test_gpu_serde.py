@@ -353,3 +353,29 @@ def test_gqa_long_context_shape_decodes_streams_the_oracle_encoded(oracle):
     # the same blobs through the pickle, one by one
     got = de.from_bytes(blobs[1].to_bytes())
     assert (bits_np(kv_rows(got)) == wants[1]).all()
+
+
+def test_blob_writer_and_loader_on_cuda_tensors_agree_with_pickle():
+    """to_bytes / from_bytes against plain pickle on an encoded chunk whose tensors are on the GPU."""
+    import io
+    import pickle
+    from cachegen_b200.serde.cachegen_basics import CacheGenGPUEncoderOutput
+    from cachegen_b200.synth import generate_kv
+    kv = generate_kv(32, 2, 128, 300, seed=8, device="cuda", dtype=torch.float16)
+    ser, de = make_serde(512, "vllm", out_dtype=torch.float16)
+    eo = ser.encode(kv)
+    f = io.BytesIO()
+    pickle.dump(eo, f)
+    blob = eo.to_bytes()
+    assert blob == f.getvalue()
+    back, plain = CacheGenGPUEncoderOutput.from_bytes(blob), pickle.load(io.BytesIO(blob))
+    assert back.cdf.is_cuda and torch.equal(back.cdf, plain.cdf) and torch.equal(back.max_tensors_key, plain.max_tensors_key)
+    for a, b in zip(back.data_chunks, plain.data_chunks):
+        assert torch.equal(a.bytestream, b.bytestream) and torch.equal(a.bytestream_lengths, b.bytestream_lengths)
+    assert torch.equal(de.from_bytes(blob), de.decode(eo))
+    # two loads in a row share the thread's staging memory: the first one's tensors must survive the second
+    first = CacheGenGPUEncoderOutput.from_bytes(blob)
+    second = CacheGenGPUEncoderOutput.from_bytes(ser.to_bytes(kv * 0.5))
+    torch.cuda.synchronize()
+    assert torch.equal(first.cdf, plain.cdf) and torch.equal(first.data_chunks[1].bytestream, plain.data_chunks[1].bytestream)
+    assert not torch.equal(second.max_tensors_key, first.max_tensors_key)
