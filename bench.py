@@ -417,7 +417,7 @@ def run_ours(args, spec):
             host_chunks, h2d, "the same call on the tensors of the reference's blob (int16 tables, int32 lengths) in pinned host memory")
         del host_chunks
         # (3) the reference's wire format itself: pickled blobs through from_bytes, a few chunks
-        nb = min(4, len(chunks))
+        nb = min(8, len(chunks))
         blobs = [eo.to_bytes() for eo in chunks[:nb]]
         torch.cuda.synchronize()
         t0 = time.perf_counter()
@@ -429,7 +429,25 @@ def run_ours(args, spec):
                                       "value": nb * kv_bytes / len(chunks) / dt / 1e9, "unit": "GB/s",
                                       "what": "CacheGenDeserializer.from_bytes on the reference-format pickle, chunk by "
                                               "chunk, wall clock: the load of the blob (30 MB per chunk through pinned staging) dominates"}
+        de.from_bytes_many(blobs)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        de.from_bytes_many(blobs)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        extra["from_bytes_many_pickle"] = {"ms_per_chunk": 1e3 * dt / nb, "value": nb * kv_bytes / len(chunks) / dt / 1e9,
+                                           "unit": "GB/s", "what": f"CacheGenDeserializer.from_bytes_many on {nb} such blobs"}
         del blobs
+        ser.to_bytes(kv_chunk0)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(3):
+            blob_len = len(ser.to_bytes(kv_chunk0))
+        dt = (time.perf_counter() - t0) / 3
+        extra["to_bytes_pickle"] = {"ms_per_chunk": 1e3 * dt, "blob_bytes_per_chunk": blob_len,
+                                    "value": kv_chunk0.numel() * 2 / dt / 1e9, "unit": "GB/s",
+                                    "what": "CacheGenSerializer.to_bytes of one chunk (KV on the GPU) to the "
+                                            "reference-format pickle, wall clock"}
         # (4) the two decoder layouts on one chunk's first sub-chunk: symbols only, same inputs and output
         from cachegen_b200 import torchac_cuda as tcu
         eo, dc = chunks[0], chunks[0].data_chunks[0]

@@ -249,7 +249,10 @@ def dump_blob(eo: "CacheGenGPUEncoderOutput") -> bytes:
             raw_of[id(t)] = memoryview(t.reshape(-1).view(torch.uint8).numpy()) if t.numel() else b""
     out = _PartsWriter()
     _BlobPickler(out, raw_of).dump(eo)
-    return b"".join(out.parts)
+    blob = b"".join(out.parts)
+    if on_gpu:
+        st.end()
+    return blob
 
 
 # `CacheGenEncoderOutput.from_bytes` is what the reference's tests call on a blob
@@ -326,26 +329,36 @@ def _load_storage_fast(b):
 
 
 class _Staging:
-    """Pinned host memory that a thread's blob loads pass through on their way to the GPU: the bytes
-    are copied into it by torch's multi-threaded CPU copy and leave it by an asynchronous copy on the
-    current stream, several times faster than a copy from pageable memory.  One per thread, grown on
-    demand; `begin` waits until the copies of the previous load have left it."""
+    """Pinned host memory that a thread's blob loads and dumps pass through: bytes are copied into it
+    by torch's multi-threaded CPU copy and leave it by an asynchronous copy on the current stream
+    (or arrive in it from the GPU), several times faster than a copy to or from pageable memory.
+    Two buffers per thread, used in turn and grown on demand, so that filling one overlaps the
+    copies still leaving the other; `begin` waits until the chosen buffer's last copies are done."""
 
     def __init__(self):
+        self.bufs = [None, None]
+        self.events = [None, None]
+        self.turn = 0
         self.buf = None
         self.pos = 0
-        self.done = None
 
     def begin(self, nbytes: int) -> None:
-        if self.done is not None:
-            self.done.synchronize()
-            self.done = None
-        self.pos = 0
-        if self.buf is None or self.buf.numel() < nbytes:
-            self.buf = None
-            self.buf = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8)
+        self.turn ^= 1
+        i = self.turn
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+            self.events[i] = None
+        if self.bufs[i] is None or self.bufs[i].numel() < nbytes:
+            self.bufs[i] = None
+            self.bufs[i] = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8)
             if torch.cuda.is_available():
-                self.buf = self.buf.pin_memory()
+                self.bufs[i] = self.bufs[i].pin_memory()
+        self.buf = self.bufs[i]
+        self.pos = 0
+
+    def end(self) -> None:
+        """Storages loaded outside a blob load do not pass through the staging memory."""
+        self.buf = None
 
     def to_device(self, view_cpu: torch.Tensor, device) -> torch.Tensor:
         n = view_cpu.numel()
@@ -356,8 +369,8 @@ class _Staging:
         stage.copy_(view_cpu)
         out = torch.empty(n, dtype=torch.uint8, device=device)
         out.copy_(stage, non_blocking=True)
-        self.done = torch.cuda.Event()
-        self.done.record(torch.cuda.current_stream(device))
+        self.events[self.turn] = torch.cuda.Event()
+        self.events[self.turn].record(torch.cuda.current_stream(device))
         return out
 
 
@@ -438,7 +451,7 @@ def load_blob(bs):
             return _Unpickler(f).load()
     finally:
         if staged:
-            _staging().pos = _staging().buf.numel()  # storages loaded outside a blob load do not use it
+            _staging().end()
 
 
 def _adopt_reference_module_path():

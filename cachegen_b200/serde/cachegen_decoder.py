@@ -481,6 +481,14 @@ class CacheGenDeserializer(Deserializer):
                 status.zero_()
                 raise RuntimeError("cachegen decode: " + _lib.status_text(bits))
 
+    def from_bytes_many(self, blobs: List[bytes], out: torch.Tensor = None) -> torch.Tensor:
+        """from_bytes for the blobs of consecutive chunks of one KV cache: one result tensor, as
+        decode_many builds it; each blob is loaded while the copies of the one before are still on
+        their way to the GPU."""
+        chunks = [flat_format.from_bytes(b) if flat_format.is_flat(b) else CacheGenGPUEncoderOutput.from_bytes(b)
+                  for b in blobs]
+        return self.decode_many(chunks, out=out)
+
     def from_bytes(self, bs: bytes) -> torch.Tensor:
         if flat_format.is_flat(bs):
             return self.decode(flat_format.from_bytes(bs))  # a CGB2 container: one copy to the GPU, decoded in place

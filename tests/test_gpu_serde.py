@@ -379,3 +379,20 @@ def test_blob_writer_and_loader_on_cuda_tensors_agree_with_pickle():
     torch.cuda.synchronize()
     assert torch.equal(first.cdf, plain.cdf) and torch.equal(first.data_chunks[1].bytestream, plain.data_chunks[1].bytestream)
     assert not torch.equal(second.max_tensors_key, first.max_tensors_key)
+
+
+def test_from_bytes_many_equals_from_bytes_chunk_by_chunk():
+    from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
+    from cachegen_b200.serde import CacheGenSerializer
+    from cachegen_b200.synth import generate_kv
+    kv = generate_kv(32, 2, 128, 256 * 5, seed=12, device="cuda", dtype=torch.float16)
+    ser, de = make_serde(256, "vllm", out_dtype=torch.float16)
+    flat_ser = CacheGenSerializer(LMCacheEngineConfig.from_defaults(chunk_size=256),
+                                  LMCacheEngineMetadata(model_name=MODEL_7B, world_size=1, worker_id=0, fmt="vllm"),
+                                  wire_format="flat")
+    parts = [kv[:, :, s:s + 256] for s in range(0, kv.shape[2], 256)]
+    blobs = [(flat_ser if i == 2 else ser).to_bytes(p) for i, p in enumerate(parts)]   # one CGB2 container among pickles
+    want = torch.cat([de.from_bytes(b) for b in blobs], dim=2)
+    got = de.from_bytes_many(blobs)
+    de.check_status()
+    assert torch.equal(got, want)
