@@ -231,7 +231,7 @@ def dump_blob(eo: "CacheGenGPUEncoderOutput") -> bytes:
     raw_of = {}
     on_gpu = [t for t in fast if t.is_cuda and t.numel()]
     if on_gpu:
-        st = _staging()
+        st = staging()
         sizes = [t.numel() * t.element_size() for t in on_gpu]
         st.begin(sum((n + 255) // 256 * 256 for n in sizes))
         pos, slices = 0, []
@@ -324,7 +324,7 @@ def _load_storage_fast(b):
         if device.type == "cpu":
             raw = view_cpu.clone()
         else:
-            raw = _staging().to_device(view_cpu, device)
+            raw = staging().to_device(view_cpu, device)
     return torch.storage.TypedStorage(wrap_storage=raw.untyped_storage(), dtype=dtype, _internal=True)
 
 
@@ -374,10 +374,32 @@ class _Staging:
         return out
 
 
+    def whole_to_device(self, view_cpu: torch.Tensor, device) -> torch.Tensor:
+        """One host buffer (any memory) to the GPU through the staging memory."""
+        self.begin(view_cpu.numel())
+        try:
+            return self.to_device(view_cpu, device)
+        finally:
+            self.end()
+
+    def whole_from_device(self, t: torch.Tensor) -> bytes:
+        """The bytes of a contiguous GPU tensor: one asynchronous copy into the staging memory, one
+        synchronisation, one copy into the result."""
+        flat = t.reshape(-1).view(torch.uint8)
+        self.begin(flat.numel())
+        try:
+            stage = self.buf[:flat.numel()]
+            stage.copy_(flat, non_blocking=True)
+            torch.cuda.current_stream(t.device).synchronize()
+            return bytes(memoryview(stage.numpy()))
+        finally:
+            self.end()
+
+
 _staging_local = threading.local()
 
 
-def _staging() -> _Staging:
+def staging() -> _Staging:
     st = getattr(_staging_local, "staging", None)
     if st is None:
         st = _staging_local.staging = _Staging()
@@ -443,7 +465,7 @@ def load_blob(bs):
     staged = False
     try:
         if torch.cuda.is_available():
-            _staging().begin(len(bs))
+            staging().begin(len(bs))
             staged = True
         return _ViewUnpickler(bs).load()
     except Exception:
@@ -451,7 +473,7 @@ def load_blob(bs):
             return _Unpickler(f).load()
     finally:
         if staged:
-            _staging().end()
+            staging().end()
 
 
 def _adopt_reference_module_path():

@@ -485,12 +485,14 @@ class CacheGenDeserializer(Deserializer):
         """from_bytes for the blobs of consecutive chunks of one KV cache: one result tensor, as
         decode_many builds it; each blob is loaded while the copies of the one before are still on
         their way to the GPU."""
-        chunks = [flat_format.from_bytes(b) if flat_format.is_flat(b) else CacheGenGPUEncoderOutput.from_bytes(b)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        chunks = [flat_format.from_bytes(b, device=dev) if flat_format.is_flat(b) else CacheGenGPUEncoderOutput.from_bytes(b)
                   for b in blobs]
         return self.decode_many(chunks, out=out)
 
     def from_bytes(self, bs: bytes) -> torch.Tensor:
         if flat_format.is_flat(bs):
-            return self.decode(flat_format.from_bytes(bs))  # a CGB2 container: one copy to the GPU, decoded in place
+            # a CGB2 container: one copy to the GPU, decoded in place
+            return self.decode(flat_format.from_bytes(bs, device=torch.device("cuda", torch.cuda.current_device())))
         # tensors pickled on a GPU come back on that GPU; anything else is staged by the decode plan
         return self.decode(CacheGenGPUEncoderOutput.from_bytes(bs))

@@ -221,7 +221,10 @@ class FlatChunk:
         return FlatChunk(self.blob.cpu().pin_memory(), self.header)
 
     def tobytes(self) -> bytes:
-        return self.blob.cpu().numpy().tobytes()
+        if self.blob.is_cuda:
+            from .cachegen_basics import staging
+            return staging().whole_from_device(self.blob)  # through pinned memory
+        return self.blob.numpy().tobytes()
 
     # -- section views (same device as the blob)
     def _view(self, off: int, nbytes: int, dtype: torch.dtype) -> torch.Tensor:
@@ -258,8 +261,17 @@ class FlatChunk:
 
 
 def from_bytes(buf, device=None) -> FlatChunk:
-    """Wraps a bytes-like CGB2 container; with `device` the bytes are copied there."""
+    """Wraps a bytes-like CGB2 container; with `device` the bytes are copied there (to a GPU through
+    pinned staging memory, straight from `buf`)."""
     header = FlatHeader.parse(buf)
+    device = torch.device(device) if device is not None else None
+    if device is not None and device.type == "cuda":
+        import warnings
+        from .cachegen_basics import staging
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")  # a read-only buffer, and it is only read
+            view = torch.frombuffer(buf, dtype=torch.uint8)
+        return FlatChunk(staging().whole_to_device(view, device), header)
     t = torch.frombuffer(bytearray(buf) if isinstance(buf, bytes) else buf, dtype=torch.uint8)
     chunk = FlatChunk(t, header)
     return chunk.to(device) if device is not None else chunk
