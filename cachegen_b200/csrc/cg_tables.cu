@@ -91,6 +91,7 @@ extern "C" int cg_pack_sparse_tables(const uint8_t *counts, const int64_t *count
     if ((reinterpret_cast<uintptr_t>(masks_out) & 3) || (reinterpret_cast<uintptr_t>(group_off_out) & 3))
         return CG_E_ALIGN;
     const int nslab = (nchannels + kGroup - 1) / kGroup;
+    if (static_cast<int64_t>(nrows) * nslab >= (int64_t{1} << 30)) return CG_E_SHAPE;  // offsets are uint32 counts
     const dim3 grid(nslab, nrows);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     sparse_masks_kernel<<<grid, kGroup, 0, st>>>(counts, count_row_off, bins, nchannels,
