@@ -459,11 +459,13 @@ class CacheGenDeserializer(Deserializer):
         return [w["status"] for w in self._workspace.get("groups", []) if "status" in w]
 
     def plan(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None,
-             peer_out: bool = False) -> DecodePlan:
+             peer_out: bool = False, workspace: dict = None) -> DecodePlan:
         """The launch plan decode_many would run, for callers that decode the same chunks repeatedly.
-        peer_out: `out` lives on another GPU of the box (see DecodePlan)."""
+        peer_out: `out` lives on another GPU of the box (see DecodePlan).  Plans built on one workspace
+        (default: this object's) share its offset buffer: `run` recomputes the offsets every time, but
+        `run_decode` alone is only valid while no other plan of the workspace has run in between."""
         return DecodePlan(encoder_outputs, self._bins_on(_device_of(encoder_outputs[0])), self.fmt, self.out_dtype,
-                          out=out, workspace=self._workspace, peer_out=peer_out)
+                          out=out, workspace=self._workspace if workspace is None else workspace, peer_out=peer_out)
 
     def _bins_on(self, dev) -> torch.Tensor:
         if not dev.type == "cuda":
