@@ -133,13 +133,13 @@ def copy_token_range_async(dst: torch.Tensor, src: torch.Tensor, stream: torch.c
     to the same range of another such tensor (`dst`, possibly memory of another GPU obtained from
     buffer_on_root) with one two-dimensional asynchronous copy on `stream`: 2L rows of (t1 - t0)*H*D
     elements, T*H*D elements apart.  The copy engines move it, no kernel runs."""
-    from cuda.bindings import runtime as cudart
     if src.shape != dst.shape or src.dtype != dst.dtype or src.dim() != 5 or src.shape[1] != 2:
         raise RuntimeError("expected two [L, 2, t, H, D] views of the same shape and type")
     L, _, t, H, D = src.shape
     for x in (src, dst):
         if x.stride(4) != 1 or x.stride(3) != D or x.stride(2) != H * D or x.stride(0) != 2 * x.stride(1):
             raise RuntimeError("views must be token ranges of contiguous [L, 2, T, H, D] tensors")
+    from cuda.bindings import runtime as cudart
     esz = src.element_size()
     err, = cudart.cudaMemcpy2DAsync(dst.data_ptr(), dst.stride(1) * esz, src.data_ptr(), src.stride(1) * esz,
                                     t * H * D * esz, 2 * L, cudart.cudaMemcpyKind.cudaMemcpyDeviceToDevice,

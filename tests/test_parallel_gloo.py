@@ -70,3 +70,22 @@ def test_two_gloo_ranks_shard_and_deliver():
             assert agree_all is True
             assert agree_one_bad is False   # rank 1 reported a failure: nobody proceeds
             assert part == list(range(rank * 32, rank * 32 + 32))
+
+
+def test_token_range_copy_refuses_other_layouts():
+    """The two-dimensional copy only takes token ranges of contiguous [L, 2, T, H, D] tensors (checked
+    before anything is enqueued)."""
+    import pytest
+    import torch
+    from cachegen_b200.parallel import copy_token_range_async
+    a = torch.zeros(3, 2, 16, 4, 8, dtype=torch.float16)
+    b = torch.zeros(3, 2, 16, 4, 8, dtype=torch.float16)
+    with pytest.raises(RuntimeError):
+        copy_token_range_async(a[:, :, 2:6], b[:, :, 2:7], None)              # shapes differ
+    with pytest.raises(RuntimeError):
+        copy_token_range_async(a[:, :, 2:6], b.float()[:, :, 2:6], None)      # types differ
+    with pytest.raises(RuntimeError):
+        copy_token_range_async(a.permute(0, 1, 3, 2, 4)[:, :, :, 2:6].permute(0, 1, 3, 2, 4)[..., ::2],
+                               b[:, :, 2:6][..., ::2], None)                  # not a unit innermost stride
+    with pytest.raises(RuntimeError):
+        copy_token_range_async(a[:, :1, 2:6].expand(3, 2, 4, 4, 8), b[:, :, 2:6], None)   # rows not evenly spaced
