@@ -251,7 +251,7 @@ def run_ours(args, spec):
     from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
     from cachegen_b200.serde import CacheGenDeserializer, CacheGenSerializer
     from cachegen_b200.serde.cachegen_basics import CacheGenGPUBytestream, CacheGenGPUEncoderOutput
-    from cachegen_b200.parallel import copy_token_range_async, buffer_on_root, gather_layers, max_over_ranks, partition
+    from cachegen_b200.parallel import PipelinedDelivery, buffer_on_root, gather_layers, max_over_ranks, partition
     from cachegen_b200.serde.cachegen_basics import CacheGenConfig
     from cachegen_b200.synth import generate_kv
 
@@ -361,31 +361,13 @@ def run_ours(args, spec):
             shared = buffer_on_root((L_total, 2, T, H, D), torch.float16, root=0)
             full_out = shared if rank == 0 else None
             target = shared[mine.start:mine.stop]
-            nparts = min(args.parts, len(chunks))
-            per = (len(chunks) + nparts - 1) // nparts
-            parts, t0, parts_ws = [], 0, {}
-            for i in range(0, len(chunks), per):
-                tn = sum(c.max_tensors_key.shape[1] for c in chunks[i:i + per])
-                dst_local = (target if rank == 0 else out)[:, :, t0:t0 + tn]
-                parts.append((de.plan(chunks[i:i + per], out=dst_local, workspace=parts_ws), t0, tn))
-                t0 += tn
-            copy_stream = torch.cuda.Stream(device=dev)
-            delivery = (f"decode in {len(parts)} parts; each part's token range is copied to GPU 0's blob over NVLink "
+            pipe = PipelinedDelivery(de, chunks, out, target, parts=args.parts, target_is_local=(rank == 0))
+            delivery = (f"decode in {len(pipe.parts)} parts; each part's token range is copied to GPU 0's blob over NVLink "
                         "(cudaMemcpy2DAsync on a second stream) while the next part is decoded")
-
-            def step():
-                cur = torch.cuda.current_stream(dev)
-                for part_plan, a, n in parts:
-                    part_plan.run()
-                    if rank != 0:
-                        done = torch.cuda.Event()
-                        done.record(cur)
-                        copy_stream.wait_event(done)
-                        copy_token_range_async(target[:, :, a:a + n], out[:, :, a:a + n], copy_stream)
-                cur.wait_stream(copy_stream)
+            step = pipe.run
             step()
             barrier()
-            assert int(parts_ws["status"].item()) == 0, "a part's decode reported a problem"
+            assert pipe.status() == 0, "a part's decode reported a problem"
             check = gather_layers(out if rank != 0 else target.contiguous(), L_total, root=0)
             if rank == 0:
                 assert torch.equal(check, full_out), "copied KV differs from the gathered KV"

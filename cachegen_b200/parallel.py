@@ -145,3 +145,45 @@ def copy_token_range_async(dst: torch.Tensor, src: torch.Tensor, stream: torch.c
                                     t * H * D * esz, 2 * L, cudart.cudaMemcpyKind.cudaMemcpyDeviceToDevice,
                                     stream.cuda_stream)
     _cuda_check(err, "cudaMemcpy2DAsync")
+
+
+class PipelinedDelivery:
+    """Decode a rank's chunks of one KV cache and deliver the result into a blob on another GPU of the
+    box, overlapped: the chunks are decoded in `parts` parts into the rank's own slab `local`
+    ([L_rank, 2, T, H, D]); as soon as a part is decoded its token range is copied into `target` (the
+    rank's layers of the consumer's blob, from buffer_on_root) on a second stream while the next part
+    is decoded.  When `target` is this GPU's own memory the parts decode straight into it.
+
+    `deserializer`: a CacheGenDeserializer in "vllm" layout; `chunks`: its encoded chunks, in token
+    order.  `run()` enqueues everything; the caller's current stream waits for the copies at the end."""
+
+    def __init__(self, deserializer, chunks: list, local: torch.Tensor, target: torch.Tensor, parts: int = 8,
+                 target_is_local: bool = False):
+        self.dev = local.device
+        self.local, self.target, self.direct = local, target, target_is_local
+        self.copy_stream = torch.cuda.Stream(device=self.dev)
+        self.workspace = {}
+        nparts = max(1, min(parts, len(chunks)))
+        per = (len(chunks) + nparts - 1) // nparts
+        self.parts, t0 = [], 0
+        for i in range(0, len(chunks), per):
+            group = chunks[i:i + per]
+            tn = sum(c.num_tokens if hasattr(c, "num_tokens") else c.max_tensors_key.shape[1] for c in group)
+            dst = (target if target_is_local else local)[:, :, t0:t0 + tn]
+            self.parts.append((deserializer.plan(group, out=dst, workspace=self.workspace), t0, tn))
+            t0 += tn
+
+    def run(self) -> None:
+        cur = torch.cuda.current_stream(self.dev)
+        for plan, a, n in self.parts:
+            plan.run()
+            if not self.direct:
+                done = torch.cuda.Event()
+                done.record(cur)
+                self.copy_stream.wait_event(done)
+                copy_token_range_async(self.target[:, :, a:a + n], self.local[:, :, a:a + n], self.copy_stream)
+        cur.wait_stream(self.copy_stream)
+
+    def status(self) -> int:
+        """The parts' status word (synchronises); 0 = nothing reported."""
+        return int(self.workspace["status"].item()) if "status" in self.workspace else 0
