@@ -52,10 +52,10 @@ def parse_args():
     ap.add_argument("--shard", default="requests", choices=["requests", "layers"],
                     help="N > 1: one request per GPU (weak scaling, default) or the layers of ONE request "
                          "split across the GPUs and the decoded KV gathered to GPU 0 over NCCL (strong scaling)")
-    ap.add_argument("--deliver", default="nccl", choices=["nccl", "peer", "copy"],
-                    help="--shard layers: gather the decoded slabs with NCCL after the decode (default), let "
-                         "every decode kernel store straight into GPU 0's blob over NVLink (CUDA IPC mapping), "
-                         "or decode in --parts parts and copy each to GPU 0's blob while the next is decoded")
+    ap.add_argument("--deliver", default="copy", choices=["copy", "nccl", "peer"],
+                    help="--shard layers: decode in --parts parts and copy each to GPU 0's blob while the next is "
+                         "decoded (default), gather the decoded slabs with NCCL after the decode, or let every "
+                         "decode kernel store straight into GPU 0's blob over NVLink (CUDA IPC mapping)")
     ap.add_argument("--parts", type=int, default=8, help="--deliver copy: parts a rank's chunks are decoded in")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
