@@ -36,6 +36,31 @@ def do_dequantize(t: torch.Tensor, bins: torch.Tensor, maxtensors: torch.Tensor)
     return t
 
 
+def bytes_to_tensor(bs: bytes, device="cuda") -> torch.Tensor:
+    """A byte string as a uint8 tensor on `device` (dec.py:37-41); to a GPU through pinned staging."""
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")  # a read-only buffer, and it is only read
+        view = torch.frombuffer(bs, dtype=torch.uint8)
+    device = torch.device(device)
+    if device.type == "cuda":
+        device = torch.device("cuda", torch.cuda.current_device() if device.index is None else device.index)
+        return CGBasics.staging().whole_to_device(view, device)
+    return view.clone()
+
+
+def recombine_bytes(bytes_tensor: torch.Tensor, output_lengths: torch.Tensor) -> torch.Tensor:
+    """Back-to-back streams as padded rows [nlayers, nchannels, 256] for decode_fast_new
+    (dec.py:43-49): row (r, c) holds the 256 bytes that start where stream (r, c) starts, reading
+    no further than the last byte of `bytes_tensor`.  The legacy layout; from_bytes does not use it."""
+    width = CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK
+    lengths = output_lengths.reshape(-1).to(torch.int64)
+    starts = lengths.cumsum(0) - lengths
+    index = starts[:, None] + torch.arange(width, device=starts.device)
+    index.clamp_(max=bytes_tensor.numel() - 1)
+    return bytes_tensor[index].reshape(*output_lengths.shape, width)
+
+
 def decode_chunk(cdf: torch.Tensor, data_chunk: CacheGenGPUBytestream, target_buffer: torch.Tensor) -> None:
     """Symbols of one sub-chunk into target_buffer [2L, ntokens, C] uint8, strided ok (dec.py:53-75)."""
     lengths = data_chunk.bytestream_lengths

@@ -43,6 +43,81 @@ def _split_kv(tensor: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return torch.unbind(tensor.reshape(num_layers, 2, num_tokens, num_heads * head_size), dim=1)
 
 
+def torch_quant_vectorized(bins: torch.Tensor, input_groups: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The reference's quantiser with its own signature (enc.py:42-59), on the quantise kernel: bins
+    [R] (any numeric type), input_groups [R, T, C] float16 / bfloat16 on the GPU -> (symbols int8
+    [R, T, C], max|x| per (row, token) [R, T, 1] in the input's dtype).  The serializer does not go
+    through here (it quantises K and V of the blob in place, tables in the same pass)."""
+    if input_groups.dim() != 3 or input_groups.dtype not in _DTYPES or not input_groups.is_cuda:
+        raise TypeError("expected a CUDA float16 / bfloat16 tensor [nlayers, ntokens, nchannels]")
+    x = input_groups.contiguous()
+    R, T, C = x.shape
+    if bins.numel() != R:
+        raise RuntimeError(f"bins describe {bins.numel()} rows, the input has {R}")
+    b = bins.to(device=x.device, dtype=torch.float32).contiguous()
+    if R % 2:  # the kernel takes rows in two halves: give an odd count one more row to chew on
+        x = torch.cat((x, x[-1:]))
+        b = torch.cat((b, b[-1:]))
+    half = x.shape[0] // 2
+    max_bins = max(int(b.max()), 1)
+    sym = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scales = torch.empty(x.shape[:2], dtype=x.dtype, device=x.device)
+    cdf = torch.empty((x.shape[0], C, max_bins + 1), dtype=torch.int16, device=x.device)
+    null = ctypes.c_void_p(None)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().cg_quantize_cdf(_ptr(x), _DTYPES[x.dtype], T * C, half * T * C, C, C, half, T, 1, C, _ptr(b),
+                                        max_bins, _ptr(sym), _ptr(scales), _ptr(cdf), null, null, null,
+                                        _stream(x.device))
+    _lib.check(rc, "cg_quantize_cdf")
+    return sym[:R], scales[:R].unsqueeze(-1)
+
+
+def concat_max(max1) -> torch.Tensor:
+    """A sequence of per-layer max tensors as one tensor with a leading layer axis (enc.py:62-70)."""
+    return torch.stack([max1[i] for i in range(len(max1))])
+
+
+def collect_bytes(output_buffer: torch.Tensor, output_lengths: torch.Tensor) -> torch.Tensor:
+    """The first output_lengths[r, c] bytes of every row output_buffer[r, c, :], back to back in
+    (r, c) order, as one uint8 tensor (enc.py:210-222), on the offset and compaction kernels."""
+    if output_buffer.dim() != 3 or output_buffer.dtype != torch.uint8 or not output_buffer.is_cuda:
+        raise TypeError("expected a CUDA uint8 buffer [nlayers, nchannels, row]")
+    buf, lengths = output_buffer.contiguous(), output_lengths.to(torch.int32).contiguous()
+    NL, C, stride = buf.shape
+    if tuple(lengths.shape) != (NL, C):
+        raise RuntimeError("output_lengths must have shape [nlayers, nchannels]")
+    dev = buf.device
+    total, outside = torch.stack((lengths.sum(dtype=torch.int64),
+                                  ((lengths < 0) | (lengths > stride)).sum(dtype=torch.int64))).tolist()
+    if outside:
+        raise RuntimeError("collect_bytes: a length is negative or exceeds the buffer's row size")
+    nslab = (C + _lib.CG_GROUP_CHANNELS - 1) // _lib.CG_GROUP_CHANNELS
+    group_off = torch.empty(NL * nslab, dtype=torch.int64, device=dev)
+    sub_off = torch.tensor([0, total], dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.empty(total, dtype=torch.uint8, device=dev)
+    job = _lib.DecodeJob()
+    job.lengths, job.nbytes, job.length_kind = lengths.data_ptr(), total, _lib.CG_LENGTHS_I32
+    with torch.cuda.device(dev):
+        rc = _lib.lib().cg_decode_offsets((_lib.DecodeJob * 1)(job), 1, NL, C, _ptr(group_off), _ptr(status), _stream(dev))
+        _lib.check(rc, "cg_decode_offsets")
+        rc = _lib.lib().cg_compact_streams(_ptr(buf), stride, _ptr(lengths), _ptr(group_off), _ptr(sub_off), 1, NL, C,
+                                           _ptr(out), _stream(dev))
+        _lib.check(rc, "cg_compact_streams")
+    if int(status.item()):
+        raise RuntimeError("collect_bytes: " + _lib.status_text(int(status.item())))
+    return out
+
+
+def encode_ntokens(cdf_int: torch.Tensor, encode_input: torch.Tensor, output_buffer: torch.Tensor,
+                   output_lengths: torch.Tensor) -> torch.Tensor:
+    """encode_fast_new into the caller's buffers, then collect_bytes (enc.py:225-242)."""
+    from .. import torchac_cuda
+    torchac_cuda.encode_fast_new(cdf_int, encode_input, output_buffer, output_lengths)
+    torchac_cuda.check_status(cdf_int.device)
+    return collect_bytes(output_buffer, output_lengths)
+
+
 def row_scales(kv: torch.Tensor) -> torch.Tensor:
     """max|x| over the channels of every (row, token): [2L, T] in kv.dtype, key rows then value rows
     (the max1 of torch_quant_vectorized, enc.py:55).  It does not depend on the bin settings."""

@@ -214,3 +214,45 @@ def test_warp_per_stream_decoder_rejects_long_tables(tc):
     out = torch.zeros((1, 8, 4), dtype=torch.uint8, device="cuda")
     with pytest.raises(RuntimeError):
         tc.decode_fast_prefsum_warp(cdf, torch.zeros(8, dtype=torch.uint8, device="cuda"), pref, out)
+
+
+def test_reference_named_helpers_around_the_entry_points(oracle, tc):
+    """torch_quant_vectorized, encode_ntokens / collect_bytes, recombine_bytes and bytes_to_tensor with
+    the reference's signatures (cachegen_encoder.py:42-59,210-242, cachegen_decoder.py:37-49): the
+    legacy padded-row path end to end against the oracle."""
+    from cachegen_b200.serde import cachegen_decoder as D
+    from cachegen_b200.serde import cachegen_encoder as E
+    rng = np.random.default_rng(77)
+    R, T, C = 5, 100, 200                     # an odd row count and a ragged channel count
+    bins = np.array([32, 16, 16, 8, 32], dtype=np.float32)
+    x = (rng.standard_normal((R, T, C)) * rng.lognormal(0, 0.5, (R, 1, C))).astype(np.float16)
+    x[2, 7] = 0                               # an all-zero token row: symbol 0 everywhere
+    xq, max1 = E.torch_quant_vectorized(torch.from_numpy(bins).cuda(), torch.from_numpy(x).cuda())
+    want_sym, want_max = oracle.quantize(x.view(np.uint16), bins, oracle.F16)
+    assert xq.dtype == torch.int8 and tuple(max1.shape) == (R, T, 1)
+    assert (xq.cpu().numpy() == want_sym).all()
+    assert (max1.cpu().numpy().view(np.uint16).reshape(R, T) == want_max.reshape(R, T)).all()
+    assert torch.equal(E.concat_max([max1[i] for i in range(R)]), max1)
+
+    cdf_t = tc.calculate_cdf(xq, 32)
+    cdf = oracle.calculate_cdf(want_sym, 32)
+    buf = torch.zeros((R, C, 256), dtype=torch.uint8, device="cuda")
+    lens = torch.zeros((R, C), dtype=torch.int32, device="cuda")
+    stream_bytes = E.encode_ntokens(cdf_t, xq, buf, lens)
+    want_bytes, want_len = oracle.encode_chunk(cdf, want_sym)
+    assert (lens.cpu().numpy() == want_len).all()
+    assert stream_bytes.cpu().numpy().tobytes() == want_bytes.tobytes()
+    with pytest.raises(RuntimeError):
+        E.collect_bytes(buf, lens + 300)      # lengths beyond the row are refused, not followed
+
+    wire = D.bytes_to_tensor(stream_bytes.cpu().numpy().tobytes())
+    assert wire.is_cuda and torch.equal(wire, stream_bytes)
+    rows = D.recombine_bytes(wire, lens)
+    assert tuple(rows.shape) == (R, C, 256)
+    flat, starts = want_bytes, np.concatenate(([0], np.cumsum(want_len.reshape(-1))[:-1]))
+    pick = np.minimum(starts[:, None] + np.arange(256), flat.size - 1)
+    assert (rows.cpu().numpy().reshape(-1, 256) == flat[pick]).all()
+    out = torch.zeros((R, T, C), dtype=torch.uint8, device="cuda")
+    tc.decode_fast_new(cdf_t, rows, lens, out)
+    tc.check_status()
+    assert (out.cpu().numpy() == want_sym.view(np.uint8)).all()
