@@ -206,3 +206,24 @@ def test_blob_writer_gives_the_bytes_of_pickle_dump():
         want = t._typed_storage().__reduce__()[1][0]   # torch's own stream of this storage
         head = B._legacy_stream_head(dt, str(t.untyped_storage()._cdata), "cpu", t.numel())
         assert head + bytes(memoryview(t.view(torch.uint8).numpy())) == want
+
+
+def test_a_c_program_links_against_the_header_and_the_library(tmp_path):
+    """gcc compiles tests/abi_link/c_client.c against include/cachegen_b200.h, links it with the
+    library and runs it: no Python, no torch between a caller and the ABI."""
+    import os
+    import shutil
+    import subprocess
+    from cachegen_b200 import _lib
+    if shutil.which("gcc") is None:
+        pytest.skip("no gcc")
+    _lib.lib()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    libdir = os.path.dirname(_lib.LIB_PATH)
+    exe = str(tmp_path / "c_client")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.join(root, "include"),
+                    os.path.join(root, "tests", "abi_link", "c_client.c"), "-o", exe,
+                    "-L", libdir, "-l:" + os.path.basename(_lib.LIB_PATH), "-Wl,-rpath," + libdir], check=True)
+    run = subprocess.run([exe], capture_output=True, text=True)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "all checks passed" in run.stdout
