@@ -227,3 +227,4 @@ def test_a_c_program_links_against_the_header_and_the_library(tmp_path):
     run = subprocess.run([exe], capture_output=True, text=True)
     assert run.returncode == 0, run.stdout + run.stderr
     assert "all checks passed" in run.stdout
+    assert ctypes.sizeof(_lib.DecodeJob) == 96   # the ctypes mirror has the size the C program checked
