@@ -164,10 +164,14 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
         const int64_t off_masks = (static_cast<int64_t>(nrows) * p.nslab + 1) * 4 + 15 & ~int64_t{15};
         const int64_t off_counts = off_masks + (__ldg(job.table_row_off + nrows) + 15 & ~int64_t{15});
         uint32_t mask = 0;
+        bool inside = true;
         if (active) {
-            const uint8_t *mrow = base + off_masks + __ldg(job.table_row_off + row);
-            mask = 2 * cq <= 16 ? __ldg(reinterpret_cast<const uint16_t *>(mrow) + c)
-                                : __ldg(reinterpret_cast<const uint32_t *>(mrow) + c);
+            const int width = 2 * cq <= 16 ? 2 : 4;
+            const int64_t at_mask = off_masks + __ldg(job.table_row_off + row) + static_cast<int64_t>(c) * width;
+            inside = at_mask >= 0 && at_mask + width <= job.tables_nbytes;
+            if (inside)
+                mask = width == 2 ? __ldg(reinterpret_cast<const uint16_t *>(base + at_mask))
+                                  : __ldg(reinterpret_cast<const uint32_t *>(base + at_mask));
             if (2 * cq < 32) mask &= (1u << (2 * cq)) - 1u;
         }
         __syncthreads();  // warp_sums is free again
@@ -175,7 +179,7 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
         const int64_t at = off_counts +
                            __ldg(reinterpret_cast<const uint32_t *>(base) + static_cast<int64_t>(row) * p.nslab + blockIdx.x) +
                            before;
-        const bool fits = off_counts <= job.tables_nbytes && at + __popc(mask) <= job.tables_nbytes;
+        const bool fits = inside && off_counts <= job.tables_nbytes && at + __popc(mask) <= job.tables_nbytes;
         if (!fits && active && p.status) atomicOr(p.status, CG_S_BAD_TABLE);
         if (active)
             stage_table_column_from_sparse(smem, mask, fits ? base + at : nullptr, cq, job.scale_stride, p.lp,
