@@ -38,6 +38,14 @@ CG_HD int cg_clz(uint32_t x) {
     return x ? __builtin_clz(x) : 32;
 #endif
 }
+// x << n, 0 for n >= 32 (what the device's shift instruction gives)
+CG_HD uint32_t cg_shl(uint32_t x, uint32_t n) {
+#if defined(__CUDA_ARCH__)
+    return x << n;
+#else
+    return n >= 32u ? 0u : x << n;
+#endif
+}
 // upper 32 bits of (hi:lo) << (s & 31)
 CG_HD uint32_t cg_fshl(uint32_t lo, uint32_t hi, uint32_t s) {
 #if defined(__CUDA_ARCH__)
@@ -136,13 +144,13 @@ struct BitWindow {
     uint32_t hi, mid, lo;  // unread bits, hi's top bit first
     int nbits;             // valid bits in hi:mid:lo
 
+    // word j of the stream, big-endian, bits past the stream's end cleared; no branches
     CG_HD uint32_t fetch(uint32_t j) const {
         const uint32_t b0 = j * 32u;
-        if (b0 >= end_bit) return 0u;
-        uint32_t w = cg_bswap32(cg_load_stream_word(wp + j));
-        const uint32_t rem = end_bit - b0;
-        if (rem < 32u) w &= 0xFFFFFFFFu << (32u - rem);
-        return w;
+        uint32_t w = 0u;
+        if (b0 < end_bit) w = cg_bswap32(cg_load_stream_word(wp + j));
+        const uint32_t rem = end_bit - b0;  // >= 2^31 (clamped to 32 below) when the word lies past the end
+        return w & ~cg_fshr_clamp(0xFFFFFFFFu, 0u, rem);
     }
     // returns the stream's first 32 bits (the coder's initial `value`, dec_new.cu:257)
     CG_HD uint32_t open(const uint8_t *p, uint32_t len) {
@@ -166,19 +174,34 @@ struct BitWindow {
         nbits -= static_cast<int>(s);
     }
     CG_HD bool low_water() const { return nbits <= 32; }
+    // fewer valid bits than one symbol can take: a range update shifts by at most 18 bits when the
+    // table is strictly increasing (the updated interval spans at least 2^14 values)
+    CG_HD bool short_of_bits() const { return nbits < 18; }
+    // Tops the window up with the whole words that fit (none above 64 valid bits, one above 32, two
+    // otherwise), straight-line: every lane of the warp runs the same instructions whatever it needs.
     CG_HD void refill() {
-        while (nbits <= 64) {
-            const uint32_t w = fetch(next++);
-            const uint32_t p = static_cast<uint32_t>(nbits < 0 ? 0 : nbits);  // nothing valid below position p
-            if (p < 32u) {
-                hi |= cg_fshr_clamp(w, 0u, p);
-                mid |= cg_fshl_clamp(0u, w, 32u - p);
-            } else {
-                mid |= cg_fshr_clamp(w, 0u, p - 32u);
-                lo |= cg_fshl_clamp(0u, w, 64u - p);
-            }
-            nbits = static_cast<int>(p) + 32;
+        const uint32_t p = static_cast<uint32_t>(nbits < 0 ? 0 : nbits);  // nothing valid below position p
+        const uint32_t k = p <= 32u ? 2u : (p <= 64u ? 1u : 0u);
+        uint32_t wa = fetch(next), wb = fetch(next + 1u);
+        if (k < 2u) wb = 0u;
+        if (k < 1u) wa = 0u;
+        // (wa:wb) goes to bit position p of hi:mid:lo, whose bits from p on are zero
+        const uint32_t q = p & 31u;
+        const uint32_t t0 = cg_fshr_clamp(wa, 0u, q);        // wa >> q
+        const uint32_t t1 = cg_fshr_clamp(wb, wa, q);        // low word of (wa:wb) >> q
+        const uint32_t t2 = cg_fshl_clamp(0u, wb, 32u - q);  // wb << (32 - q), 0 for q == 0
+        if (p < 32u) {
+            hi |= t0;
+            mid |= t1;
+            lo |= t2;
+        } else if (p < 64u) {  // one word fits past position 32, or two exactly at it (q == 0: t1 == wb)
+            mid |= t0;
+            lo |= t1;
+        } else {  // a word fits only at position 64 exactly (wa is 0 beyond it)
+            lo |= t0;
         }
+        nbits = static_cast<int>(p + 32u * k);
+        next += k;
     }
 };
 
@@ -245,6 +268,24 @@ struct DecoderState {
     }
 };
 
+// The same update for the decode_streams loop: no "| 1" guards on the two leading-zero counts.  With a
+// strictly increasing table the updated interval spans at least 2^14 values, so neither operand can be
+// zero; on a corrupt table a count of 32 only makes the shifts below wrap, and every later read stays
+// inside the table column and the stream.
+CG_HD void update_unguarded(DecoderState &st, uint32_t flo, uint32_t fhi, BitWindow &bw) {
+    st.offset -= flo;
+    st.low += flo;
+    st.span32 = fhi - flo;
+    const uint32_t high = st.low + st.span32 - 1u;
+    const uint32_t n1 = static_cast<uint32_t>(cg_clz(st.low ^ high));
+    const uint32_t y = cg_shl((~st.low) | high, n1);  // top bit set: low has 0 and high 1 at the first bit they differ in
+    const uint32_t s = n1 + static_cast<uint32_t>(cg_clz(y + y));
+    st.low = cg_fshl(0u, st.low, s);
+    st.span32 = cg_fshl(0u, st.span32, s);
+    st.offset = cg_fshl(bw.hi, st.offset, s);
+    bw.consume(s);
+}
+
 // One stream.  col: address of the stream's table column, entries cdf << 16, rows kTableRowBytes apart,
 // one readable row past the last symbol's; emit(a) receives, token after token, the address of the
 // decoded symbol's table entry (symbol = (a - col) / kTableRowBytes).  lanes: the warp's lanes that
@@ -305,6 +346,127 @@ CG_HD void decode_stream(Smem sm, uint32_t col, int maxsym, const uint8_t *strea
     }
     if (cg_any_lane(lanes, bw.low_water())) bw.refill();
     exact_step(false);
+}
+
+// ---- decode loop, NS streams per lane, search depth chosen by the caller ---------------------------------
+// Exact search with a run-time depth (the rare path of decode_streams).
+CG_HD uint32_t exact_search(Smem sm, uint32_t col, uint32_t a_max, uint32_t span32, uint32_t target, int levels) {
+    uint32_t a = col;
+    for (int b = levels - 1; b >= 0; --b) {
+        const uint32_t ca = a + (static_cast<uint32_t>(kTableRowBytes) << b);
+        const bool ok = ca <= a_max;
+        const bool take = ok && (scale_exact(span32, sm.ld(ok ? ca : a)) <= target);
+        a = take ? ca : a;
+    }
+    return a;
+}
+
+// Smallest search depth whose top entry, 2^depth - 1, lies above every symbol 0 .. nsym-1, kept
+// within [2, full_levels].
+CG_HD int fast_levels_for(int nsym, int full_levels) {
+    int fl = 2;
+    while (fl < full_levels && (1 << fl) - 1 < nsym) fl++;
+    return fl;
+}
+
+// NS streams of one lane decoded side by side (same token count, same table length), the fast
+// search limited to the first 2^FL table entries.
+//
+// The caller picks FL from what it knows about the symbols (a row quantised to `bins` bins holds
+// symbols 0 .. bins-2, so 2^FL >= bins is enough); the result never depends on that choice: a fast
+// search that ends on or above entry D = min(2^FL - 1, maxsym) -- the only way a symbol >= D, a
+// symbol that starts from the full 2^32 range (span32 == 0 makes every comparison true) or a probe
+// of a padding entry can show -- is thrown away and the whole warp repeats that symbol with the
+// exact, full-depth search.  Entries above maxsym must be staged as 0xFFFFFFFF (never "<= offset"
+// unless offset is span-1, which then lands above D) and the column needs 2^FL + 1 readable rows.
+//   col[i]    table column of stream i (see decode_stream)
+//   det       address threshold of entry D: column-independent because a column's offset inside a
+//             table row is below kTableRowBytes (det = table base + D * kTableRowBytes)
+//   emit(a, t4)  receives the NS table-entry addresses of one token's symbols and four times the
+//             token's index (ntok >= 1)
+template <int FL, int NS, class Emit>
+CG_HD void decode_streams(Smem sm, const uint32_t (&col)[NS], uint32_t det, int maxsym, int full_levels,
+                          const uint8_t *const (&stream)[NS], const uint32_t (&len)[NS], int ntok, uint32_t lanes,
+                          Emit emit) {
+    static_assert(FL >= 2, "the first two levels are held in registers");
+    BitWindow bw[NS];
+    DecoderState st[NS];
+    uint32_t r_mid[NS], r_lo[NS], r_hi[NS], a_max[NS], col_top[NS];
+    constexpr uint32_t kTop = static_cast<uint32_t>(kTableRowBytes) << (FL - 1);
+    constexpr uint32_t kHalf = kTop >> 1;
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+    for (int i = 0; i < NS; ++i) {
+        st[i].low = 0u;
+        st[i].span32 = 0u;
+        st[i].offset = bw[i].open(stream[i], len[i]);
+        a_max[i] = col[i] + static_cast<uint32_t>(maxsym) * kTableRowBytes;
+        col_top[i] = col[i] + kTop;
+        r_mid[i] = sm.ld(col[i] + kTop);
+        r_lo[i] = sm.ld(col[i] + kHalf);
+        r_hi[i] = sm.ld(col[i] + kTop + kHalf);
+    }
+    uint32_t a[NS];
+    // One back edge and one vote per token: the rare path (a refill of the bit windows, or the exact
+    // search when the fast one cannot be trusted) only tops the windows up or replaces the symbol and
+    // its scaled bounds; the range update below is shared.
+    const uint32_t last4 = static_cast<uint32_t>(ntok - 1) * 4u;
+    uint32_t t4 = 0u;  // four times the token index: the caller's emit indexes 4-byte per-token data with it
+    for (; t4 != last4; t4 += 4u) {
+        uint32_t flo[NS], fhi[NS];
+        bool rare = false;  // a lane short of bits, or a search that ended on or above entry D
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+        for (int i = 0; i < NS; ++i) {
+            const bool t1 = cg_umulhi(st[i].span32, r_mid[i]) <= st[i].offset;
+            uint32_t x = t1 ? col_top[i] : col[i];
+            x = cg_umulhi(st[i].span32, t1 ? r_hi[i] : r_lo[i]) <= st[i].offset ? x + kHalf : x;
+            a[i] = FastSearch<FL - 3>::run(sm, x, st[i].span32, st[i].offset);
+            rare = rare || a[i] >= det || bw[i].short_of_bits();
+            flo[i] = cg_umulhi(st[i].span32, sm.ld(a[i]));
+            fhi[i] = cg_umulhi(st[i].span32, sm.ld(a[i] + kTableRowBytes));
+        }
+        if (cg_any_lane(lanes, rare)) {
+            bool low = false, odd = false;
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+            for (int i = 0; i < NS; ++i) {
+                low = low || bw[i].short_of_bits();
+                odd = odd || a[i] >= det;
+            }
+            if (cg_any_lane(lanes, low)) {
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+                for (int i = 0; i < NS; ++i) bw[i].refill();
+            }
+            if (cg_any_lane(lanes, odd)) {
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+                for (int i = 0; i < NS; ++i) {
+                    a[i] = exact_search(sm, col[i], a_max[i], st[i].span32, st[i].offset, full_levels);
+                    flo[i] = scale_exact(st[i].span32, sm.ld(a[i]));
+                    fhi[i] = (a[i] == a_max[i]) ? st[i].span32
+                                                : scale_exact(st[i].span32, sm.ld(a[i] + kTableRowBytes));
+                }
+            }
+        }
+        emit(a, t4);
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+        for (int i = 0; i < NS; ++i) update_unguarded(st[i], flo[i], fhi[i], bw[i]);
+    }
+    // last symbol: no range update (dec_new.cu:273-275), so no new bits either
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+    for (int i = 0; i < NS; ++i) a[i] = exact_search(sm, col[i], a_max[i], st[i].span32, st[i].offset, full_levels);
+    emit(a, t4);
 }
 
 // ---- MSB-first bit writer into one scratch row (add_bits_to_output, enc_new.cu:21-97) ---------------------

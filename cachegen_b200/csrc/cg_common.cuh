@@ -44,13 +44,16 @@ __device__ __forceinline__ uint32_t smem_addr(const void *p) {
 // ---- table staging ----------------------------------------------------------------------------
 // Every thread owns one (row, channel) table.  It is kept in shared memory as tab[m][tid] =
 // cdf[m] << 16 so that lane i always hits bank i, whatever entry m each lane is at.  Each thread
-// fills (and later reads) only its own column, so no block barrier is needed.
+// fills (and later reads) only its own column, so no block barrier is needed.  Only the entries of
+// the symbols, 0 .. lp-2, are staged; the rows above them hold kTablePadding, which a search step
+// of the decoder takes for "above the target" (see decode_streams in cg_coder.cuh).
+constexpr uint32_t kTablePadding = 0xFFFFFFFFu;
 __device__ __forceinline__ void stage_table_column(uint32_t *tab, const int16_t *cdf_row, int lp,
                                                    int rows, int tid) {
-    const int n = lp < rows ? lp : rows;
+    const int n = lp - 1 < rows ? lp - 1 : rows;
     for (int m = 0; m < n; ++m)
         tab[m * kGroup + tid] = static_cast<uint32_t>(static_cast<uint16_t>(__ldg(cdf_row + m))) << 16;
-    for (int m = n; m < rows; ++m) tab[m * kGroup + tid] = 0u;
+    for (int m = n; m < rows; ++m) tab[m * kGroup + tid] = kTablePadding;
 }
 
 // The same column from the byte counts of the non-centre symbols (CG_TABLES_COUNTS):
@@ -67,7 +70,7 @@ __device__ __forceinline__ void stage_table_column_from_counts(uint32_t *tab, co
     const uint32_t total = static_cast<uint32_t>(ntokens) & 0xFFFFu;
     const bool pow2 = (total & (total - 1u)) == 0u;
     const int sh = 31 - __clz(static_cast<int>(total | 1u));
-    const int n = lp < rows ? lp : rows;
+    const int n = lp - 1 < rows ? lp - 1 : rows;
     uint32_t cum = 0;
     for (int i = 0; i < n; ++i) {
         const uint32_t prod = scale * (cum & 0xFFFFu);
@@ -79,7 +82,7 @@ __device__ __forceinline__ void stage_table_column_from_counts(uint32_t *tab, co
         else if (i <= 2 * cq) count = __ldg(cnt + (i - 1) * stride);
         cum += count;
     }
-    for (int i = n; i < rows; ++i) tab[i * kGroup + tid] = 0u;
+    for (int i = n; i < rows; ++i) tab[i * kGroup + tid] = kTablePadding;
 }
 
 // The same column from the sparse byte counts (CG_TABLES_SPARSE): `mask` has bit j set when stored
@@ -97,7 +100,7 @@ __device__ __forceinline__ void stage_table_column_from_sparse(uint32_t *tab, ui
     const uint32_t total = static_cast<uint32_t>(ntokens) & 0xFFFFu;
     const bool pow2 = (total & (total - 1u)) == 0u;
     const int sh = 31 - __clz(static_cast<int>(total | 1u));
-    const int n = lp < rows ? lp : rows;
+    const int n = lp - 1 < rows ? lp - 1 : rows;
     uint32_t cum = 0;
     for (int i = 0; i < n; ++i) {
         const uint32_t prod = scale * (cum & 0xFFFFu);
@@ -112,12 +115,13 @@ __device__ __forceinline__ void stage_table_column_from_sparse(uint32_t *tab, ui
         }
         cum += count;
     }
-    for (int i = n; i < rows; ++i) tab[i * kGroup + tid] = 0u;
+    for (int i = n; i < rows; ++i) tab[i * kGroup + tid] = kTablePadding;
 }
 
-// ---- block-wide exclusive scan over kGroup (=128) ints ------------------------------------------
-// warp_sums: shared int[4].  Returns the exclusive prefix of `v` across the block.
-__device__ __forceinline__ int block_exclusive_scan_128(int v, int *warp_sums, int tid, int *total) {
+// ---- block-wide exclusive scan over 32 * NWARPS ints --------------------------------------------
+// warp_sums: shared int[NWARPS].  Returns the exclusive prefix of `v` across the block.
+template <int NWARPS>
+__device__ __forceinline__ int block_exclusive_scan(int v, int *warp_sums, int tid, int *total) {
     const int lane = tid & 31, w = tid >> 5;
     int incl = v;
 #pragma unroll
@@ -129,13 +133,16 @@ __device__ __forceinline__ int block_exclusive_scan_128(int v, int *warp_sums, i
     __syncthreads();
     int base = 0, all = 0;
 #pragma unroll
-    for (int i = 0; i < kGroup / 32; ++i) {
+    for (int i = 0; i < NWARPS; ++i) {
         const int s = warp_sums[i];
         if (i < w) base += s;
         all += s;
     }
     if (total) *total = all;
     return base + incl - v;
+}
+__device__ __forceinline__ int block_exclusive_scan_128(int v, int *warp_sums, int tid, int *total) {
+    return block_exclusive_scan<kGroup / 32>(v, warp_sums, tid, total);
 }
 
 template <int DT> struct Half16;

@@ -32,6 +32,8 @@ __global__ void __launch_bounds__(kGroup) decode_symbols_kernel(const SymDecodeP
     const int tid = threadIdx.x;
     const int row = blockIdx.y;
     const int c = blockIdx.x * kGroup + tid;
+    // the lanes that decode together, taken while the warp is still converged
+    const uint32_t lanes = __ballot_sync(0xFFFFFFFFu, c < p.nchannels);
     if (c >= p.nchannels) return;  // no block barrier in this kernel
     const int64_t g = static_cast<int64_t>(row) * p.nchannels + c;
     int64_t start, len;
@@ -61,7 +63,7 @@ __global__ void __launch_bounds__(kGroup) decode_symbols_kernel(const SymDecodeP
         o += o1;
     };
     decode_stream<LEVELS, POW2>(Smem{}, col, p.lp - 2, p.bytes + start, static_cast<uint32_t>(len), p.ntokens,
-                                __activemask(), emit);
+                                lanes, emit);
 }
 
 // ---- one warp per stream (kept for comparison) -------------------------------------------------------------
@@ -130,6 +132,7 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
     const int row = blockIdx.y;
     const int c = blockIdx.x * kGroup + tid;
     const bool active = c < p.nchannels;
+    const uint32_t lanes = __ballot_sync(0xFFFFFFFFu, active);  // taken while the warp is still converged
     const int ntok = job.ntokens;
     const int layer = row % p.nlayers, kv = row / p.nlayers;
     const int64_t g = static_cast<int64_t>(row) * p.nchannels + c;
@@ -144,6 +147,7 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
     if (len > (1 << 20)) { len = 1 << 20; bad = true; }
     const int excl = block_exclusive_scan_128(len, warp_sums, tid, nullptr);
     int64_t start = __ldg(job.group_off + static_cast<int64_t>(row) * p.nslab + blockIdx.x) + excl;
+    if (start < 0) { start = 0; len = 0; bad = true; }
     if (start > job.nbytes) { start = job.nbytes; bad = true; }
     if (start + len > job.nbytes) { len = static_cast<int>(job.nbytes - start); bad = true; }
     if (bad && active && p.status) atomicOr(p.status, CG_S_BAD_LENGTHS);
@@ -187,8 +191,11 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
     } else if (active) {
         if (job.table_kind == CG_TABLES_COUNTS) {
             const int cq = static_cast<int>(half_range(__ldg(p.bins + row)));
-            const uint8_t *cnt = static_cast<const uint8_t *>(job.tables) + __ldg(job.table_row_off + row) + c;
-            stage_table_column_from_counts(smem, cnt, p.nchannels, cq, job.scale_stride, p.lp, rows + 1, tid);
+            const int64_t at = __ldg(job.table_row_off + row) + c;
+            const bool fits = cq >= 0 && at >= 0 && at + static_cast<int64_t>(2 * cq - 1) * p.nchannels < job.tables_nbytes;
+            if (!fits && p.status) atomicOr(p.status, CG_S_BAD_TABLE);
+            stage_table_column_from_counts(smem, static_cast<const uint8_t *>(job.tables) + (fits ? at : 0), p.nchannels,
+                                           fits ? cq : 0, job.scale_stride, p.lp, rows + 1, tid);
         } else {
             stage_table_column(smem, static_cast<const int16_t *>(job.tables) + g * p.lp, p.lp, rows + 1, tid);
         }
@@ -214,7 +221,192 @@ __global__ void __launch_bounds__(kGroup) decode_dequant_kernel(const __grid_con
         sc_a += 4u;
     };
     decode_stream<LEVELS, POW2>(Smem{}, col, p.lp - 2, job.bytes + start, static_cast<uint32_t>(len), ntok_r,
-                                __activemask(), emit);
+                                lanes, emit);
+}
+
+// ---- the same with NS adjacent channels per thread ----------------------------------------------------------
+// A block still covers one 128-channel group of one row, with 128 / NS threads: thread t decodes
+// channels NS*t .. NS*t + NS-1 side by side (NS independent dependency chains per thread; loop
+// control, the warp vote and the token's scale are paid once per NS symbols) and writes their 16-bit
+// values with one 2*NS-byte store.  Channel NS*t + i keeps its table in column t + i * (128 / NS), so a
+// warp still reads 32 different banks whatever entries its lanes are at.  The search depth is chosen
+// per block from the row's bin count (see decode_streams); the result does not depend on it.
+// Needs a head size and output strides that are multiples of NS and output pointers aligned to 2*NS bytes.
+template <int OUT_DT>
+__device__ __forceinline__ uint32_t pack_pair(float v0, float v1);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<CG_F16>(float v0, float v1) {
+    const __half2 h = __floats2half2_rn(v0, v1);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<CG_BF16>(float v0, float v1) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// Shared memory (the tables) allows 12 blocks per SM at the usual table length of 33; asking for no
+// more leaves the compiler 80 registers a thread, which it needs to interleave the NS chains.
+constexpr int kMultiBlocksPerSM = 12;
+
+template <int NS, int OUT_DT>
+__global__ void __launch_bounds__(kGroup / NS, kMultiBlocksPerSM)
+decode_dequant_multi_kernel(const __grid_constant__ FusedDecodeParams p, int scale_dt, int full_levels) {
+    constexpr int kThreads = kGroup / NS;
+    constexpr int kWarps = kThreads / 32;
+    extern __shared__ uint32_t smem[];
+    __shared__ float scale_f[kSubTokens];
+    __shared__ float lut[CG_MAX_LP];
+    __shared__ int warp_sums[kWarps];
+
+    const cg_decode_job &job = p.jobs[blockIdx.z];
+    const int tid = threadIdx.x;
+    const int row = blockIdx.y;
+    const int c0 = blockIdx.x * kGroup + NS * tid;  // nchannels is a multiple of NS: all NS channels exist or none
+    const bool active = c0 < p.nchannels;
+    const uint32_t lanes = __ballot_sync(0xFFFFFFFFu, active);
+    const int ntok = job.ntokens;
+    const int layer = row % p.nlayers, kv = row / p.nlayers;
+    const int64_t g = static_cast<int64_t>(row) * p.nchannels + c0;
+
+    // stream offsets: group base + exclusive scan of this block's lengths (cachegen_decoder.py:70)
+    int len[NS];
+    bool bad = false;
+    int len_sum = 0;
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        len[i] = 0;
+        if (active)
+            len[i] = job.length_kind == CG_LENGTHS_U16
+                         ? static_cast<int>(__ldg(static_cast<const uint16_t *>(job.lengths) + g + i))
+                         : __ldg(static_cast<const int32_t *>(job.lengths) + g + i);
+        if (len[i] < 0) { len[i] = 0; bad = true; }
+        if (len[i] > (1 << 20)) { len[i] = 1 << 20; bad = true; }
+        len_sum += len[i];
+    }
+    const int excl = block_exclusive_scan<kWarps>(len_sum, warp_sums, tid, nullptr);
+    int64_t start[NS];
+    start[0] = __ldg(job.group_off + static_cast<int64_t>(row) * p.nslab + blockIdx.x) + excl;
+#pragma unroll
+    for (int i = 1; i < NS; ++i) start[i] = start[i - 1] + len[i - 1];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        if (start[i] < 0) { start[i] = 0; len[i] = 0; bad = true; }
+        if (start[i] > job.nbytes) { start[i] = job.nbytes; bad = true; }
+        if (start[i] + len[i] > job.nbytes) { len[i] = static_cast<int>(job.nbytes - start[i]); bad = true; }
+    }
+    if (bad && active && p.status) atomicOr(p.status, CG_S_BAD_LENGTHS);
+
+    // per-token scales of this row and the row's (s - Cq) / Cq table (cachegen_decoder.py:30-32)
+    const uint16_t *sc = static_cast<const uint16_t *>(kv ? job.scales_v : job.scales_k) +
+                         static_cast<int64_t>(layer) * job.scale_stride;
+    for (int t = tid; t < ntok; t += kThreads) scale_f[t] = half_bits_to_float(__ldg(sc + t), scale_dt);
+    const float cqf = half_range(__ldg(p.bins + row));
+    for (int m = tid; m < p.lp - 1; m += kThreads) lut[m] = __fdiv_rn(__fsub_rn(static_cast<float>(m), cqf), cqf);
+    const int cq = cqf >= 0.0f && cqf < 64.0f ? static_cast<int>(cqf) : 64;
+    const int rows = table_rows(p.lp, full_levels < 2 ? 2 : full_levels);  // the register levels read entries 1..3
+    uint32_t *tabs[NS];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) tabs[i] = smem + tid + i * kThreads;
+    if (job.table_kind == CG_TABLES_SPARSE) {  // the whole block: the counts are found by a scan of the masks
+        const int nrows = 2 * p.nlayers;
+        const uint8_t *base = static_cast<const uint8_t *>(job.tables);
+        const int64_t off_masks = (static_cast<int64_t>(nrows) * p.nslab + 1) * 4 + 15 & ~int64_t{15};
+        const int64_t off_counts = off_masks + (__ldg(job.table_row_off + nrows) + 15 & ~int64_t{15});
+        uint32_t mask[NS];
+        int nset[NS], nset_sum = 0;
+        bool inside = true;
+        const int width = 2 * cq <= 16 ? 2 : 4;
+        const int64_t at_mask = off_masks + __ldg(job.table_row_off + row) + static_cast<int64_t>(c0) * width;
+        if (active) inside = at_mask >= 0 && at_mask + NS * width <= job.tables_nbytes;
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+            mask[i] = 0;
+            if (active && inside)
+                mask[i] = width == 2 ? __ldg(reinterpret_cast<const uint16_t *>(base + at_mask) + i)
+                                     : __ldg(reinterpret_cast<const uint32_t *>(base + at_mask) + i);
+            if (2 * cq < 32) mask[i] &= (1u << (2 * cq)) - 1u;
+            nset[i] = __popc(mask[i]);
+            nset_sum += nset[i];
+        }
+        __syncthreads();  // warp_sums is free again
+        const int before = block_exclusive_scan<kWarps>(nset_sum, warp_sums, tid, nullptr);
+        int64_t at = off_counts +
+                     __ldg(reinterpret_cast<const uint32_t *>(base) + static_cast<int64_t>(row) * p.nslab + blockIdx.x) +
+                     before;
+        const bool fits = inside && off_counts <= job.tables_nbytes && at + nset_sum <= job.tables_nbytes;
+        if (!fits && active && p.status) atomicOr(p.status, CG_S_BAD_TABLE);
+        if (active) {
+#pragma unroll
+            for (int i = 0; i < NS; ++i) {
+                stage_table_column_from_sparse(tabs[i], mask[i], fits ? base + at : nullptr, cq, job.scale_stride, p.lp,
+                                               rows + 1, 0);
+                at += nset[i];
+            }
+        }
+    } else if (active) {
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+            if (job.table_kind == CG_TABLES_COUNTS) {
+                const int64_t at = __ldg(job.table_row_off + row) + c0 + i;
+                const bool fits = at >= 0 && at + static_cast<int64_t>(2 * cq - 1) * p.nchannels < job.tables_nbytes;
+                if (!fits && p.status) atomicOr(p.status, CG_S_BAD_TABLE);
+                stage_table_column_from_counts(tabs[i], static_cast<const uint8_t *>(job.tables) + (fits ? at : 0),
+                                               p.nchannels, fits ? cq : 0, job.scale_stride, p.lp, rows + 1, 0);
+            } else {
+                stage_table_column(tabs[i], static_cast<const int16_t *>(job.tables) + (g + i) * p.lp, p.lp, rows + 1, 0);
+            }
+        }
+    }
+    __syncthreads();
+    if (!active) return;
+
+    const int h = c0 / p.head_size, d = c0 - h * p.head_size;
+    uint16_t *o = static_cast<uint16_t *>(job.out) + layer * p.o_layer + kv * p.o_kv + h * p.o_head + d;
+    uint32_t col[NS];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) col[i] = smem_addr(tabs[i]);
+    // entry m of the row's (s - Cq)/Cq table is at lut + 4m = (a >> 7) + lut_k for an entry address a
+    // of column 0, because a - col is a multiple of 512; column i starts 4 * kThreads bytes further,
+    // which adds kThreads / 32 to (a >> 7)
+    uint32_t lut_k = smem_addr(lut) - (col[0] >> 7);
+    int64_t o_token = p.o_token;
+    uint32_t sc_a = smem_addr(scale_f);
+    int ntok_r = ntok;
+    // keep the loop's invariants in registers instead of re-deriving them from kernel parameters
+    asm volatile("" : "+l"(o_token), "+r"(lut_k), "+r"(sc_a), "+r"(ntok_r));
+    auto emit = [&](const uint32_t (&a)[NS], uint32_t) {
+        // ((sym - Cq) / Cq) * max in fp32, then one round-to-nearest cast (cachegen_decoder.py:30-33,171-173)
+        const float s = ldsf32(sc_a);
+        float v[NS];
+#pragma unroll
+        for (int i = 0; i < NS; ++i) v[i] = __fmul_rn(ldsf32((a[i] >> 7) + lut_k - i * (kThreads / 32)), s);
+        if (NS == 2) {
+            *reinterpret_cast<uint32_t *>(o) = pack_pair<OUT_DT>(v[0], v[1]);
+        } else {
+            *reinterpret_cast<uint2 *>(o) = make_uint2(pack_pair<OUT_DT>(v[0], v[1]), pack_pair<OUT_DT>(v[2 % NS], v[3 % NS]));
+        }
+        o += o_token;
+        sc_a += 4u;
+    };
+    const int maxsym = p.lp - 2;
+    const int fl = fast_levels_for(2 * cq + 1, full_levels);
+    const int top = (1 << fl) - 1;
+    const uint32_t det = smem_addr(smem) + static_cast<uint32_t>(top < maxsym ? top : maxsym) * kRowBytes;
+    const uint8_t *streams[NS];
+    uint32_t lens[NS];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) {
+        streams[i] = job.bytes + start[i];
+        lens[i] = static_cast<uint32_t>(len[i]);
+    }
+    switch (fl) {
+    case 2: decode_streams<2, NS>(Smem{}, col, det, maxsym, full_levels, streams, lens, ntok_r, lanes, emit); break;
+    case 3: decode_streams<3, NS>(Smem{}, col, det, maxsym, full_levels, streams, lens, ntok_r, lanes, emit); break;
+    case 4: decode_streams<4, NS>(Smem{}, col, det, maxsym, full_levels, streams, lens, ntok_r, lanes, emit); break;
+    case 5: decode_streams<5, NS>(Smem{}, col, det, maxsym, full_levels, streams, lens, ntok_r, lanes, emit); break;
+    default: decode_streams<6, NS>(Smem{}, col, det, maxsym, full_levels, streams, lens, ntok_r, lanes, emit); break;
+    }
 }
 
 // ---- launch helpers -------------------------------------------------------------------------------------
@@ -273,6 +465,26 @@ static int launch_fused(const FusedDecodeParams &p, cudaStream_t st) {
     return check_launch();
 }
 
+// The NS-channels-per-thread kernel needs the NS channels of a thread in one head and aligned packed stores.
+static bool multi_layout_ok(const FusedDecodeParams &p, int ns) {
+    if ((p.head_size | p.o_layer | p.o_kv | p.o_token | p.o_head) & (ns - 1)) return false;
+    for (int j = 0; j < p.njobs; ++j)
+        if (reinterpret_cast<uintptr_t>(p.jobs[j].out) & (2 * ns - 1)) return false;
+    return true;
+}
+
+template <int NS, int OUT_DT>
+static int launch_fused_multi(const FusedDecodeParams &p, int scale_dt, cudaStream_t st) {
+    const int full = search_levels(p.lp);
+    const size_t smem = table_bytes(p.lp, full < 2 ? 2 : full);
+    const dim3 grid(p.nslab, 2 * p.nlayers, p.njobs), block(kGroup / NS);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(decode_dequant_multi_kernel<NS, OUT_DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(smem));
+    decode_dequant_multi_kernel<NS, OUT_DT><<<grid, block, smem, st>>>(p, scale_dt, full);
+    return check_launch();
+}
+
 }  // namespace cg
 
 using namespace cg;
@@ -327,18 +539,18 @@ extern "C" int cg_decode_padded(const int16_t *cdf, const uint8_t *streams, int6
     return launch_symbols<1>(p, nrows, static_cast<cudaStream_t>(stream));
 }
 
-extern "C" int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int nlayers, int nheads,
-                                 int head_size, int lp, const float *bins, int scale_dtype,
-                                 int out_dtype, int64_t o_layer, int64_t o_kv, int64_t o_token,
-                                 int64_t o_head, int32_t *status, void *stream) {
+// Checks the arguments of the fused decode and fills the kernel parameters; launches nothing.
+static int fused_params(const cg_decode_job *jobs_host, int njobs, int nlayers, int nheads, int head_size, int lp,
+                        const float *bins, int scale_dtype, int out_dtype, int64_t o_layer, int64_t o_kv,
+                        int64_t o_token, int64_t o_head, int32_t *status, FusedDecodeParams &p) {
     if (!jobs_host || !bins) return CG_E_NULL;
     if (njobs <= 0 || nlayers <= 0 || nheads <= 0 || head_size <= 0) return CG_E_SHAPE;
     if (njobs > CG_MAX_DECODE_JOBS) return CG_E_CAPACITY;
     if (lp < 2 || lp > CG_MAX_LP) return CG_E_LP;
-    if (2 * nlayers > 65535) return CG_E_SHAPE;
+    if (nlayers > 32767) return CG_E_SHAPE;  // 2 * nlayers rows are a grid dimension
+    if (static_cast<int64_t>(nheads) * head_size > 0x7FFFFFFF - kGroup) return CG_E_SHAPE;
     if ((scale_dtype != CG_F16 && scale_dtype != CG_BF16) || (out_dtype != CG_F16 && out_dtype != CG_BF16))
         return CG_E_DTYPE;
-    FusedDecodeParams p;
     p.njobs = njobs;
     p.nlayers = nlayers;
     p.nheads = nheads;
@@ -364,15 +576,33 @@ extern "C" int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int 
             if (jb.tables_nbytes < (static_cast<int64_t>(2 * nlayers) * p.nslab + 1) * 4) return CG_E_CAPACITY;
             if (reinterpret_cast<uintptr_t>(jb.tables) & 3) return CG_E_ALIGN;
         }
+        if (jb.table_kind == CG_TABLES_COUNTS && jb.tables_nbytes <= 0) return CG_E_CAPACITY;
         if (jb.ntokens <= 0 || jb.nbytes < 0) return CG_E_SHAPE;
         if (jb.ntokens > CG_MAX_TOKENS_PER_STREAM) return CG_E_TOKENS;
         p.jobs[j] = jb;
     }
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return CG_OK;
+}
+
+static int launch_fused_any(const FusedDecodeParams &p, int scale_dtype, int out_dtype, cudaStream_t st) {
+    if (multi_layout_ok(p, 2))
+        return out_dtype == CG_F16 ? launch_fused_multi<2, CG_F16>(p, scale_dtype, st)
+                                   : launch_fused_multi<2, CG_BF16>(p, scale_dtype, st);
     if (scale_dtype == CG_F16 && out_dtype == CG_F16) return launch_fused<CG_F16, CG_F16>(p, st);
     if (scale_dtype == CG_F16 && out_dtype == CG_BF16) return launch_fused<CG_F16, CG_BF16>(p, st);
     if (scale_dtype == CG_BF16 && out_dtype == CG_F16) return launch_fused<CG_BF16, CG_F16>(p, st);
     return launch_fused<CG_BF16, CG_BF16>(p, st);
+}
+
+extern "C" int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int nlayers, int nheads,
+                                 int head_size, int lp, const float *bins, int scale_dtype,
+                                 int out_dtype, int64_t o_layer, int64_t o_kv, int64_t o_token,
+                                 int64_t o_head, int32_t *status, void *stream) {
+    FusedDecodeParams p;
+    if (int rc = fused_params(jobs_host, njobs, nlayers, nheads, head_size, lp, bins, scale_dtype, out_dtype,
+                              o_layer, o_kv, o_token, o_head, status, p))
+        return rc;
+    return launch_fused_any(p, scale_dtype, out_dtype, static_cast<cudaStream_t>(stream));
 }
 
 // ---- decode without a caller-provided workspace --------------------------------------------------------------
@@ -413,6 +643,7 @@ extern "C" int cg_decode_dequant_static(const cg_decode_job *jobs_host, int njob
     if (!jobs_host || !bins) return CG_E_NULL;
     if (njobs <= 0 || nlayers <= 0 || nheads <= 0 || head_size <= 0) return CG_E_SHAPE;
     if (njobs > CG_MAX_DECODE_JOBS) return CG_E_CAPACITY;
+    if (nlayers > 32767 || static_cast<int64_t>(nheads) * head_size > 0x7FFFFFFF - kGroup) return CG_E_SHAPE;
     const int nchannels = nheads * head_size;
     const int64_t ngroups = static_cast<int64_t>(2 * nlayers) * ((nchannels + kGroup - 1) / kGroup);
     if (ngroups * njobs > CG_STATIC_OFFSET_ENTRIES) return CG_E_CAPACITY;
@@ -423,7 +654,11 @@ extern "C" int cg_decode_dequant_static(const cg_decode_job *jobs_host, int njob
         jobs[j] = jobs_host[j];
         jobs[j].group_off = scratch + j * ngroups;
     }
+    // every argument check of the fused decode comes before the first launch into the shared array
+    FusedDecodeParams p;
+    if (int rc = fused_params(jobs, njobs, nlayers, nheads, head_size, lp, bins, scale_dtype, out_dtype, o_layer,
+                              o_kv, o_token, o_head, status, p))
+        return rc;
     if (int rc = cg_decode_offsets(jobs, njobs, 2 * nlayers, nchannels, scratch, status, stream)) return rc;
-    return cg_decode_dequant(jobs, njobs, nlayers, nheads, head_size, lp, bins, scale_dtype, out_dtype,
-                             o_layer, o_kv, o_token, o_head, status, stream);
+    return launch_fused_any(p, scale_dtype, out_dtype, static_cast<cudaStream_t>(stream));
 }

@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
     const int tid = threadIdx.x;
     const int row = blockIdx.y, sub = blockIdx.z;
     const int c = blockIdx.x * kGroup + tid;
+    // the lanes that encode together, taken while the warp is still converged
+    const uint32_t lanes = __ballot_sync(0xFFFFFFFFu, c < p.nchannels);
     if (c >= p.nchannels) return;  // no block barrier in this kernel
     const int nrows = gridDim.y;
     const int64_t g = static_cast<int64_t>(row) * p.nchannels + c;
@@ -40,7 +42,6 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
     const int8_t *sp = p.sym + row * p.s0 + static_cast<int64_t>(t0) * p.s1 + c * p.s2;
     EncoderState enc;
     enc.init();
-    const uint32_t lanes = __activemask();
     bool bad_symbol = false;
 
     const int64_t s1 = p.s1;

@@ -257,7 +257,8 @@ typedef struct cg_decode_job {
     const int64_t *table_row_off; /* CG_TABLES_COUNTS: [nrows] row offsets into `tables`;
                                 CG_TABLES_SPARSE: [nrows + 1] row offsets into its masks */
     int64_t nbytes;          /* size of `bytes` */
-    int64_t tables_nbytes;   /* CG_TABLES_SPARSE only: size of `tables` */
+    int64_t tables_nbytes;   /* CG_TABLES_COUNTS and CG_TABLES_SPARSE: size of `tables` in bytes; reads
+                                are kept inside it (CG_S_BAD_TABLE otherwise) */
     int32_t ntokens;         /* tokens in this sub-chunk, 1..256 */
     int32_t scale_stride;    /* elements between consecutive layers in scales_k / scales_v
                                 (= the chunk's token count, over which its tables were built) */

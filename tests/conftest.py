@@ -52,6 +52,10 @@ def host_model():
     lib.hm_encode_stream.argtypes = [p, i, p, i, p, i64, i]
     lib.hm_decode_stream.restype = None
     lib.hm_decode_stream.argtypes = [p, i, p, i64, i, p, i]
+    lib.hm_decode_pair.restype = i
+    lib.hm_decode_pair.argtypes = [p, p, i, p, i64, p, i64, i, p, i, i]
+    lib.hm_fast_levels_for.restype = i
+    lib.hm_fast_levels_for.argtypes = [i, i]
     return lib
 
 

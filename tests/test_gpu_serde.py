@@ -396,3 +396,35 @@ def test_from_bytes_many_equals_from_bytes_chunk_by_chunk():
     got = de.from_bytes_many(blobs)
     de.check_status()
     assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("H,D", [(3, 21), (5, 26), (1, 130)])
+def test_decode_kernels_of_both_layouts_against_the_oracle(oracle, H, D):
+    """An odd head size cannot use the two-channels-per-thread kernel (its packed 32-bit stores need
+    both channels of a pair in one head): the one-channel-per-thread kernel takes over.  Even head
+    sizes that leave the last 128-channel group partly empty run the paired kernel with idle lanes."""
+    from cachegen_b200.synth import generate_kv
+    L, T = 32, 300
+    kv = generate_kv(L, H, D, T, seed=H * D, device="cpu", dtype=torch.float16)
+    ser, de = make_serde(512, "vllm", out_dtype=torch.float16)
+    eo = ser.encode(kv.cuda())
+    ref = oracle_encode(oracle, kv, ser.key_bins.cpu().numpy(), ser.value_bins.cpu().numpy(), oracle.F16)
+    for dc, (want_bytes, want_len) in zip(eo.data_chunks, ref["chunks"]):
+        assert (dc.bytestream_lengths.cpu().numpy() == want_len).all()
+        assert dc.bytestream.cpu().numpy().tobytes() == want_bytes.tobytes()
+    want = oracle.dequantize(ref["sym"].view(np.uint8), ref["bins"], ref["max"], oracle.F16, oracle.F16)
+    got = de.decode(eo)
+    de.check_status()
+    assert (bits_np(kv_rows(got)) == want).all()
+    # the same into a blob whose token stride is odd (a view of a wider allocation): no packed stores
+    wide = torch.zeros((L, 2, T, H, D + 1), dtype=torch.float16, device="cuda")
+    view = wide[..., :D]
+    from cachegen_b200.serde.cachegen_decoder import DecodePlan
+    bins = torch.cat((de.key_bins, de.value_bins))
+    try:
+        plan = DecodePlan([eo], bins, "vllm", torch.float16, out=view)
+    except RuntimeError:
+        return  # the plan insists on a contiguous blob: nothing more to check here
+    plan.run()
+    assert (bits_np(kv_rows(view.contiguous())) == want).all()
+    assert not wide[..., D].any()

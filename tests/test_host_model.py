@@ -66,3 +66,66 @@ def test_capacity_overflow_is_reported_not_written(oracle, host_model):
     assert ln == 513
     assert (out[256:] == 0xAB).all()
     assert (out[:256] == oracle.encode_stream(cdf, sym)[:256]).all()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_pair_decode_loop_matches_oracle_at_every_search_depth(oracle, host_model, seed):
+    """decode_streams (two streams per lane, fast search over the first 2^fl entries with the exact
+    search as its fallback) must give the oracle's symbols whatever depth the caller picks: too
+    shallow a depth for the symbols that occur only costs time."""
+    rng = np.random.default_rng(100 + seed)
+    for _ in range(150):
+        lp = int(rng.integers(2, 65)) if rng.random() < 0.5 else int(rng.choice([5, 9, 13, 17, 33]))
+        full = 0
+        while (1 << full) < lp - 1:
+            full += 1
+        n = int(rng.integers(1, 257))
+        maxsym = lp - 2
+        cdfs, syms, streams = [], [], []
+        for _s in range(2):
+            cdf = random_table(oracle, rng, lp, int(rng.integers(0, 2)))
+            mode = int(rng.integers(0, 4))
+            if mode == 0:
+                sym = rng.integers(0, maxsym + 1, size=n)
+            elif mode == 1:
+                sym = np.full(n, rng.integers(0, maxsym + 1))
+            elif mode == 2:  # what a row quantised to fewer bins than the table holds looks like
+                hi = int(rng.integers(0, maxsym + 1))
+                sym = rng.integers(0, hi + 1, size=n)
+            else:
+                sym = np.where(rng.random(n) < 0.9, maxsym // 2, rng.integers(0, maxsym + 1, size=n))
+            sym = sym.astype(np.int8)
+            cdfs.append(cdf)
+            syms.append(sym)
+            streams.append(oracle.encode_stream(cdf, sym))
+        off = int(rng.integers(0, 8))
+        big = rng.integers(0, 256, size=off + len(streams[0]) + len(streams[1]) + 16).astype(np.uint8)
+        big[off:off + len(streams[0])] = streams[0]
+        big[off + len(streams[0]):off + len(streams[0]) + len(streams[1])] = streams[1]
+        p0 = big.ctypes.data + off
+        p1 = p0 + len(streams[0])
+        tid = int(rng.integers(0, 64))
+        for fl in range(2, max(full, 2) + 1):
+            dec = np.zeros(2 * n, dtype=np.uint8)
+            rc = host_model.hm_decode_pair(P(cdfs[0]), P(cdfs[1]), lp, ctypes.c_void_p(p0), len(streams[0]),
+                                           ctypes.c_void_p(p1), len(streams[1]), n, P(dec), tid, fl)
+            assert rc == 0
+            assert (dec[0::2] == syms[0].view(np.uint8)).all(), (lp, fl)
+            assert (dec[1::2] == syms[1].view(np.uint8)).all(), (lp, fl)
+        # truncated streams decode as if zero-padded, like the reference's staging row
+        t0, t1 = int(rng.integers(0, len(streams[0]) + 1)), int(rng.integers(0, len(streams[1]) + 1))
+        fl = int(rng.integers(2, max(full, 2) + 1))
+        dec = np.zeros(2 * n, dtype=np.uint8)
+        host_model.hm_decode_pair(P(cdfs[0]), P(cdfs[1]), lp, ctypes.c_void_p(p0), t0, ctypes.c_void_p(p1), t1, n,
+                                  P(dec), tid, fl)
+        assert (dec[0::2] == oracle.decode_stream(cdfs[0], streams[0][:t0], n)).all()
+        assert (dec[1::2] == oracle.decode_stream(cdfs[1], big[off + len(streams[0]):off + len(streams[0]) + t1], n)).all()
+
+
+def test_search_depth_for_a_bin_count(host_model):
+    # symbols 0 .. bins-2 of a row with `bins` bins: the depth's top entry must lie above them
+    for bins, want in ((4, 2), (8, 3), (12, 4), (16, 4), (32, 5), (62, 6)):
+        nsym = 2 * (bins // 2 - 1) + 1
+        assert host_model.hm_fast_levels_for(nsym, 6) == want
+    assert host_model.hm_fast_levels_for(31, 4) == 4  # never deeper than the table
+    assert host_model.hm_fast_levels_for(1, 0) == 2   # and never below the two register levels
