@@ -15,12 +15,21 @@ standing in for real model KV.
   roofline     the dominant kernel (fused decode + dequantise + KV store) timed alone, algorithmic bytes
                over its duration against the measured HBM copy bandwidth
   cpu_baseline the CPU oracle's decode + dequantise on a bounded sample of the same chunks, all host cores
+               (and the same on one thread)
+  reference_cuda_ext  the reference's own CUDA extension (oracle/_ref, built unmodified) and the torch chain
+               around it, on one 256-token chunk of the workload on this GPU, beside this package's kernels
+  config3 / config5   the long-context GQA decode and a shortened three-quality-level encode + decode sweep
 
 With N > 1 (under torchrun) every rank decodes its own request of the same shape (weak scaling, no
-data-path collective); the time is the max over ranks and the value the sum of all ranks' bytes.
+data-path collective); the time is the max over ranks and the value the sum of all ranks' bytes.  The
+same run then measures, in the same process group, `h2d_only_ms` (the end-to-end leg's host-to-device
+copies alone) and `delivered_kv`: the Llama-70B-shape cache sharded by layers, every rank decoding its
+layers and the decoded KV delivered to GPU 0 over NVLink (pipelined copies, and NCCL after the decode).
 `--impl reference` times the CPU restatement of the reference's decode path on the host cores.
 """
 import argparse
+import glob
+import importlib.util
 import json
 import os
 import statistics
@@ -35,10 +44,18 @@ if ROOT not in sys.path:
 
 CHUNK_TOKENS = 256
 HBM_FALLBACK_GBS = 6650.0
-# DRAM bytes (read + write) of one decode_dequant_kernel launch per decoded token, Llama-7B shape,
-# 256-token chunks: 1260 MB measured by ncu on a 2,048-token launch
-# (profiles/launch_list_llama7b_2k_tokens.md); traffic grows in proportion to the tokens of a launch.
-NCU_TRAFFIC_BYTES_PER_TOKEN = {(32, 32, 128): 1259.6e6 / 2048}
+# Counters of the dominant kernel (decode_dequant_multi_kernel<2, fp16>) from ncu captures of this
+# kernel on the Llama-7B shape with 256-token chunks; they belong to the kernel as committed with this
+# file and have to be re-captured when the kernel changes.  DRAM bytes (read + write) come from a
+# 2,048-token launch and grow in proportion to the tokens of a launch; the issue figures come from a
+# 512-token launch (`--set full`, and sass__inst_executed_per_opcode).
+NCU_CAPTURE = {
+    (32, 32, 128): {"traffic_bytes_per_token": 1259.6e6 / 2048, "issue_active_pct": 64.9, "alu_pipe_pct": 59.9,
+                    "warp_instr_per_32_symbols": 56.2,
+                    "source": "ncu on bench.py --tokens 2048 (dram__bytes_read.sum + dram__bytes_write.sum) and "
+                              "--tokens 512 (--set full; sass__inst_executed_per_opcode), B200, kernel "
+                              "decode_dequant_multi_kernel<2,0>"},
+}
 
 
 def parse_args():
@@ -59,8 +76,21 @@ def parse_args():
     ap.add_argument("--parts", type=int, default=8, help="--deliver copy: parts a rank's chunks are decoded in")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true",
+                    help="skip the legs beside the headline: reference CUDA extension, configs 3 and 5 (N = 1), "
+                         "delivery of decoded KV to GPU 0 (N > 1)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work budget of the baseline sample")
     return ap.parse_args()
+
+
+def ncu_counters(L, H, D, tokens):
+    """The committed ncu figures of the dominant kernel for this shape (None when there is no capture)."""
+    cap = NCU_CAPTURE.get((L, H, D))
+    if cap is None:
+        return {}
+    return {"traffic": cap["traffic_bytes_per_token"] * tokens, "issue_active_pct": cap["issue_active_pct"],
+            "alu_pipe_pct": cap["alu_pipe_pct"], "warp_instr_per_32_symbols": cap["warp_instr_per_32_symbols"],
+            "traffic_source": cap["source"]}
 
 
 def measured_hbm_peak():
@@ -206,7 +236,9 @@ def run_cpu_baseline(spec, seconds_budget):
         d, _ = cpu_decode_pass(spec, chunks, bins, threads)
         t += d
     kv_bytes = 2 * spec["num_layers"] * spec["num_heads"] * spec["head_size"] * CHUNK_TOKENS * 2
+    one, _ = cpu_decode_pass(spec, chunks, bins, 1)  # the same chunk on a single thread
     return {"value": kv_bytes * reps / t / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "one_thread": {"value": kv_bytes / one / 1e9, "unit": "GB/s", "cores": 1, "sample": "one pass over the same chunk"},
             "tokens_per_s": CHUNK_TOKENS * reps / t,
             "sample": f"{reps} passes over one {CHUNK_TOKENS}-token chunk of the workload "
                       f"({kv_bytes / 2**20:.0f} MiB of KV each), {t:.1f} s of wall time on {threads} threads"}
@@ -236,22 +268,325 @@ def run_reference_arm(args, spec):
     line = {"impl": "reference", "metric": "decoded_kv_gbps", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32", "data": "synthetic",
-            "config": describe(spec, args), "tokens_per_s": CHUNK_TOKENS * nchunks * args.steps / total,
+            "config": dict(describe(spec, args), shard=args.shard if args.gpus > 1 else "none", delivery="none"),
+            "tokens_per_s": CHUNK_TOKENS * nchunks * args.steps / total,
             "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
 # ------------------------------------------------------------------------------------------- GPU arm
+class Harness:
+    """Timing plumbing shared by the legs: barrier + synchronise on both sides of K steps, CUDA events on
+    the current stream, max over ranks."""
+
+    def __init__(self, dev, rank, world):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.dev, self.rank, self.world = torch, dist, dev, rank, world
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def timed(self, fn, steps, warmup, local=False):
+        """ms per step.  local=True: this rank alone (no barrier, no reduction): legs only rank 0 runs."""
+        from cachegen_b200.parallel import max_over_ranks
+        torch = self.torch
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize() if local else self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize() if local else self.barrier()
+        ms = e0.elapsed_time(e1) / steps
+        return ms if local else max_over_ranks(ms, device=self.dev)
+
+
+def make_serde(spec, world, rank, cachegen_config=None, table_max_bins=None):
+    import torch
+
+    from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
+    from cachegen_b200.serde import CacheGenDeserializer, CacheGenSerializer
+    config = LMCacheEngineConfig.from_defaults(chunk_size=CHUNK_TOKENS)
+    meta = LMCacheEngineMetadata(model_name=spec["model_name"], world_size=world, worker_id=rank, fmt="vllm")
+    kw = {} if cachegen_config is None else {"cachegen_config": cachegen_config}
+    ser = CacheGenSerializer(config, meta, table_max_bins=table_max_bins, **kw)
+    de = CacheGenDeserializer(config, meta, out_dtype=torch.float16, **kw)
+    return ser, de, config, meta
+
+
+def load_reference_extension():
+    """The reference's torchac_cuda, compiled unmodified into oracle/_ref by oracle/build_ref.py."""
+    hits = glob.glob(os.path.join(ROOT, "oracle", "_ref", "torchac_cuda*.so"))
+    if not hits:
+        return None
+    spec = importlib.util.spec_from_file_location("torchac_cuda", hits[0])
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def leg_reference_cuda_ext(h, ser, de, kv_chunk, eo):
+    """One 256-token chunk of the workload through the reference's own kernels and the torch chain the
+    reference wraps around them (cachegen_decoder.py:24-34,78-112,159-173 and cachegen_encoder.py:42-59,
+    210-292 of the reference, re-typed here as the baseline), beside this package's kernels and fused
+    calls on the same inputs, same GPU, same clocks.  Inputs are valid by construction (this package's
+    encoder made them and the reference's decoder reads them back identically in the tests); the
+    reference encoder is only called when every stream fits its 256-byte shared-memory row."""
+    torch = h.torch
+    ref = load_reference_extension()
+    if ref is None:
+        return {"unavailable": "oracle/_ref/torchac_cuda*.so is not built (python oracle/build_ref.py)"}
+    import cachegen_b200.torchac_cuda as mine
+    from cachegen_b200.serde.cachegen_encoder import quantize_and_tables
+
+    L, _, T, H, D = kv_chunk.shape
+    C, NL = H * D, 2 * L
+    dc = eo.data_chunks[0]
+    cdf, lengths, payload = eo.cdf, dc.bytestream_lengths, dc.bytestream
+    key_bins, value_bins = de.key_bins.to(h.dev), de.value_bins.to(h.dev)
+    max_bins = cdf.shape[2] - 1
+    reps, warm = 10, 3
+    out = {"what": f"one {T}-token chunk ({NL * C} streams): the reference's torchac_cuda kernels, recompiled for "
+                   "sm_100, and the torch chain of its serializer classes against this package on the same inputs"}
+
+    # ---- decode: kernel against kernel
+    pref = lengths.flatten().cumsum(0).reshape(lengths.shape)
+    buf_r = torch.zeros((T, NL * C), dtype=torch.uint8, device=h.dev).reshape(NL, T, C)
+    buf_m = torch.zeros_like(buf_r)
+    k_ref = h.timed(lambda: ref.decode_fast_prefsum(cdf, payload, pref, buf_r), reps, warm, local=True)
+    k_our = h.timed(lambda: mine.decode_fast_prefsum(cdf, payload, pref, buf_m), reps, warm, local=True)
+    mine.check_status(h.dev)
+    same_symbols = bool(torch.equal(buf_r, buf_m))
+
+    # ---- decode: the reference's from_bytes after unpickling against the fused call
+    def dequantize(t, bins, maxes):
+        c = (bins // 2 - 1)[:, None, None]
+        return (t - c) / c * maxes
+
+    def ref_decode_chain():
+        ps = lengths.flatten().cumsum(0).reshape(lengths.shape)
+        ref.decode_fast_prefsum(cdf, payload, ps, buf_r)
+        key, value = buf_r.reshape(2, L, T, C).float()
+        key = dequantize(key, key_bins, eo.max_tensors_key)
+        value = dequantize(value, value_bins, eo.max_tensors_value)
+        blob = torch.stack([key, value]).reshape(2, L, T, H, D)
+        return blob.permute(1, 0, 2, 3, 4).to(torch.float16)  # the reference casts to bf16 here; fp16 to compare
+
+    out1 = torch.empty((L, 2, T, H, D), dtype=torch.float16, device=h.dev)
+    plan1 = de.plan([eo], out=out1, workspace={})
+    c_ref = h.timed(ref_decode_chain, reps, warm, local=True)
+    c_our = h.timed(plan1.run, reps, warm, local=True)
+    same_kv = bool(torch.equal(ref_decode_chain().contiguous(), out1))
+    kv_bytes = NL * T * C * 2
+    out["decode"] = {
+        "kernel_ms": {"reference_decode_fast_prefsum": k_ref, "ours_decode_fast_prefsum": k_our, "speedup": k_ref / k_our},
+        "chain_ms": {"reference_kernel_plus_torch_chain": c_ref, "ours_fused": c_our, "speedup": c_ref / c_our},
+        "decoded_kv_gbps": {"reference": kv_bytes / c_ref / 1e6, "ours": kv_bytes / c_our / 1e6},
+        "same_symbols": same_symbols, "same_kv_bits": same_kv}
+
+    # ---- encode: kernels, then the chains
+    sym, _, cdf_m = quantize_and_tables(kv_chunk, key_bins, value_bins, max_bins)
+    fits = int(lengths.max()) <= 256
+    t_cdf_ref = h.timed(lambda: (ref.calculate_cdf(sym[:L], max_bins), ref.calculate_cdf(sym[L:], max_bins)), reps, warm, local=True)
+    t_cdf_our = h.timed(lambda: (mine.calculate_cdf(sym[:L], max_bins), mine.calculate_cdf(sym[L:], max_bins)), reps, warm, local=True)
+    enc = {"calculate_cdf_ms": {"reference": t_cdf_ref, "ours": t_cdf_our, "speedup": t_cdf_ref / t_cdf_our}}
+    sbuf_r = torch.zeros((NL, C, 256), dtype=torch.uint8, device=h.dev)
+    slen_r = torch.zeros((NL, C), dtype=torch.int32, device=h.dev)
+    sbuf_m, slen_m = torch.zeros_like(sbuf_r), torch.zeros_like(slen_r)
+
+    def collect_bytes(output_buffer, output_lengths):
+        size = output_buffer.shape[-1]
+        fl, fb = output_lengths.flatten(), output_buffer.flatten()
+        summed = (size - fl).cumsum(0).roll(1)
+        summed[0] = 0
+        idx = summed.repeat_interleave(fl)
+        return fb[idx + torch.arange(len(idx), device=idx.device)]
+
+    def quant(bins, x):
+        mx = (bins // 2 - 1)[:, None, None]
+        m1 = torch.amax(torch.abs(x), dim=-1, keepdim=True)
+        return torch.round(x * (mx / m1) + mx).to(torch.int8), m1
+
+    def ref_encode_chain():
+        k, v = torch.unbind(kv_chunk.reshape(L, 2, T, C), dim=1)
+        nk, mk = quant(key_bins, k)
+        nv, mv = quant(value_bins, v)
+        enc_in = torch.cat((nk, nv), dim=0).reshape(NL, T, C)
+        tables = torch.cat([ref.calculate_cdf(nk, max_bins), ref.calculate_cdf(nv, max_bins)])
+        ob = torch.zeros((NL, C, 256), dtype=torch.uint8, device=h.dev)
+        ol = torch.zeros((NL, C), dtype=torch.int32, device=h.dev)
+        ref.encode_fast_new(tables, enc_in, ob, ol)
+        return collect_bytes(ob, ol), ol, tables
+
+    if fits:
+        t_enc_ref = h.timed(lambda: ref.encode_fast_new(cdf_m, sym, sbuf_r, slen_r), reps, warm, local=True)
+        t_enc_our = h.timed(lambda: mine.encode_fast_new(cdf_m, sym, sbuf_m, slen_m), reps, warm, local=True)
+        mine.check_status(h.dev)
+        keep = torch.arange(256, device=h.dev)[None, None, :] < slen_r[:, :, None]
+        enc["encode_fast_new_ms"] = {"reference": t_enc_ref, "ours": t_enc_our, "speedup": t_enc_ref / t_enc_our}
+        enc["same_lengths"] = bool(torch.equal(slen_r, slen_m))
+        enc["same_bytes"] = bool(torch.equal(sbuf_r[keep], sbuf_m[keep]))
+        c_enc_ref = h.timed(ref_encode_chain, 5, 2, local=True)
+        c_enc_our = h.timed(lambda: ser.encode(kv_chunk), 5, 2, local=True)
+        got_bytes, got_len, got_cdf = ref_encode_chain()
+        enc["chain_ms"] = {"reference_torch_quant_cdf_encode_collect": c_enc_ref, "ours_serializer_encode": c_enc_our,
+                           "speedup": c_enc_ref / c_enc_our}
+        enc["chain_same_payload"] = bool(torch.equal(got_bytes, payload) and torch.equal(got_len, lengths) and
+                                         torch.equal(got_cdf, cdf))
+        enc["kv_consumed_gbps"] = {"reference": kv_bytes / c_enc_ref / 1e6, "ours": kv_bytes / c_enc_our / 1e6}
+    else:
+        enc["skipped"] = "a stream of this chunk is longer than the reference encoder's 256-byte row"
+    out["encode"] = enc
+    return out
+
+
+def leg_config3(h, args):
+    """BASELINE config 3: the Mistral-7B GQA shape (32 layers x 8 KV heads x 128), 32,768 tokens, key
+    rho 0.95, decode only from pre-encoded streams on this GPU."""
+    torch = h.torch
+    from cachegen_b200.synth import WORKLOADS, generate_kv
+    spec = dict(WORKLOADS["mistral7b-gqa-32k"])
+    L, H, D, T = spec["num_layers"], spec["num_heads"], spec["head_size"], spec["num_tokens"]
+    ser, de, _, _ = make_serde(spec, 1, 0)
+    kv = generate_kv(L, H, D, T, spec["seed"], key_rho=spec["key_rho"], device=h.dev, dtype=torch.float16)
+    chunks = ser.encode_many(kv, CHUNK_TOKENS, batch=16)
+    del kv
+    out = torch.empty((L, 2, T, H, D), dtype=torch.float16, device=h.dev)
+    plan = de.plan(chunks, out=out, workspace={})
+    ms = h.timed(plan.run, max(3, args.steps // 2), 3, local=True)
+    ms_kernel = h.timed(plan.run_decode, max(3, args.steps // 2), 1, local=True)
+    de.check_status()
+    kv_bytes = 2 * L * H * D * T * 2
+    algorithmic = plan.output_bytes + plan.payload_bytes + plan.table_bytes + plan.length_bytes + plan.scale_bytes
+    peak, kind = measured_hbm_peak()
+    return {"workload": "mistral7b-gqa-32k", "tokens": T, "value": kv_bytes / ms / 1e6, "unit": "GB/s",
+            "ms_per_step": ms, "tokens_per_s": T / ms * 1e3, "launches_per_step": plan.launches,
+            "bytes_per_token": (plan.payload_bytes + plan.table_bytes + plan.length_bytes + plan.scale_bytes) / T,
+            "roofline_frac": algorithmic / ms_kernel / 1e6 / peak, "peak_kind": kind}
+
+
+def leg_config5(h, args):
+    """BASELINE config 5, shortened: requests of the Llama-7B shape, 4,096 tokens each (seeds 100..), split
+    evenly over three quality levels (default bins, half, quarter with a minimum of 4); every request is
+    encoded and decoded on this GPU.  Six requests instead of 64: the per-request work is identical."""
+    torch = h.torch
+    from cachegen_b200.serde.cachegen_basics import CacheGenConfig
+    from cachegen_b200.synth import WORKLOADS, generate_kv
+    spec = dict(WORKLOADS["llama7b-4k"])
+    L, H, D, T = spec["num_layers"], spec["num_heads"], spec["head_size"], spec["num_tokens"]
+    base = CacheGenConfig.from_model_name(spec["model_name"])
+    levels = [("default", base), ("half", base.with_bins_divided(2)), ("quarter", base.with_bins_divided(4))]
+    nreq = 6
+    kv_bytes = 2 * L * H * D * T * 2
+    out = torch.empty((L, 2, T, H, D), dtype=torch.float16, device=h.dev)
+    per_level = {}
+    enc_ms_total = dec_ms_total = 0.0
+    for i in range(nreq):
+        name, cfg = levels[i % 3]
+        ser, de, _, _ = make_serde(spec, 1, 0, cachegen_config=cfg)
+        kv = generate_kv(L, H, D, T, 100 + i, key_rho=spec["key_rho"], device=h.dev, dtype=torch.float16)
+        ser.encode_many(kv, CHUNK_TOKENS, batch=16)  # warms the allocator for this level's sizes
+        box = {}
+
+        def encode():
+            box["chunks"] = ser.encode_many(kv, CHUNK_TOKENS, batch=16)
+        ms_enc = h.timed(encode, 1, 0, local=True)
+        plan = de.plan(box["chunks"], out=out, workspace={})
+        ms_dec = h.timed(plan.run, 2, 1, local=True)
+        de.check_status()
+        wire = plan.payload_bytes + plan.table_bytes + plan.length_bytes + plan.scale_bytes
+        lv = per_level.setdefault(name, {"requests": 0, "encode_ms": 0.0, "decode_ms": 0.0, "wire_bytes": 0,
+                                         "bins": [cfg.key_first_bins, cfg.key_second_bins, cfg.key_third_bins,
+                                                  cfg.value_first_bins, cfg.value_second_bins]})
+        lv["requests"] += 1
+        lv["encode_ms"] += ms_enc
+        lv["decode_ms"] += ms_dec
+        lv["wire_bytes"] += wire
+        enc_ms_total += ms_enc
+        dec_ms_total += ms_dec
+        del kv, plan, box
+    for lv in per_level.values():
+        n = lv["requests"]
+        lv["encode_gbps"] = n * kv_bytes / lv.pop("encode_ms") / 1e6
+        lv["decode_gbps"] = n * kv_bytes / lv.pop("decode_ms") / 1e6
+        lv["bytes_per_token"] = lv.pop("wire_bytes") / (n * T)
+    return {"workload": "llama7b-4k x %d requests, seeds 100..%d, levels default / half / quarter" % (nreq, 99 + nreq),
+            "requests": nreq, "tokens_per_request": T,
+            "encode_gbps": nreq * kv_bytes / enc_ms_total / 1e6, "decode_gbps": nreq * kv_bytes / dec_ms_total / 1e6,
+            "encode_plus_decode_gbps": nreq * kv_bytes / (enc_ms_total + dec_ms_total) / 1e6,
+            "levels": per_level,
+            "what": "reference-layout chunks (int16 tables) held in HBM; bytes_per_token counts payload, tables, "
+                    "lengths and scales"}
+
+
+def leg_delivered_kv(h, args):
+    """BASELINE config 4 in the process group of the --gpus N run: the Llama-70B-shape cache (80 layers x 8
+    KV heads x 128, 16,384 tokens) sharded by layers, every rank decodes its layers and the decoded KV is
+    delivered into one blob on GPU 0 -- by pipelined peer copies while the decode runs, and by NCCL
+    send/recv after it.  Plain peer copies and NCCL only."""
+    torch = h.torch
+    from cachegen_b200.parallel import PipelinedDelivery, buffer_on_root, gather_layers, partition
+    from cachegen_b200.serde.cachegen_basics import CacheGenConfig
+    from cachegen_b200.synth import WORKLOADS, generate_kv
+    spec = dict(WORKLOADS["llama70b-gqa-16k"])
+    L_total, H, D, T = spec["num_layers"], spec["num_heads"], spec["head_size"], spec["num_tokens"]
+    mine = partition(L_total, h.world, h.rank)
+    full_cfg = CacheGenConfig.from_model_name(spec["model_name"])
+    cfg = full_cfg.layer_slice(mine.start, mine.stop)
+    ser, de, _, _ = make_serde(spec, h.world, h.rank, cachegen_config=cfg, table_max_bins=full_cfg.max_bins)
+    L = len(mine)
+    kv = generate_kv(L, H, D, T, spec["seed"], key_rho=spec["key_rho"], device=h.dev, dtype=torch.float16,
+                     first_layer=mine.start)
+    chunks = ser.encode_many(kv, CHUNK_TOKENS, batch=16)
+    del kv
+    local = torch.empty((L, 2, T, H, D), dtype=torch.float16, device=h.dev)
+    plan = de.plan(chunks, out=local, workspace={})
+    steps, warm = max(3, args.steps // 2), 2
+    total_bytes = 2 * L_total * H * D * T * 2
+    res = {"workload": "llama70b-gqa-16k", "tokens": T, "layers_per_gpu": L, "kv_bytes": total_bytes}
+
+    ms_decode = h.timed(plan.run, steps, warm)
+    res["decode_only_ms"] = ms_decode
+    # (1) NCCL after the decode
+    full_nccl = torch.empty((L_total, 2, T, H, D), dtype=torch.float16, device=h.dev) if h.rank == 0 else None
+
+    def step_nccl():
+        plan.run()
+        gather_layers(local, L_total, root=0, out=full_nccl)
+    ms_nccl = h.timed(step_nccl, steps, warm)
+    # (2) pipelined peer copies into GPU 0's blob
+    shared = buffer_on_root((L_total, 2, T, H, D), torch.float16, root=0)
+    pipe = PipelinedDelivery(de, chunks, local, shared[mine.start:mine.stop], parts=args.parts,
+                             target_is_local=(h.rank == 0))
+    ms_copy = h.timed(pipe.run, steps, warm)
+    ok_status = pipe.status() == 0
+    h.barrier()
+    same = bool(torch.equal(shared, full_nccl)) if h.rank == 0 else True
+    de.check_status()
+    res["nccl_after_decode"] = {"ms_per_step": ms_nccl, "gbps_into_gpu0": total_bytes / ms_nccl / 1e6,
+                                "what": "decode, then NCCL send/recv of every rank's layer slab to GPU 0"}
+    res["pipelined_copy"] = {"ms_per_step": ms_copy, "gbps_into_gpu0": total_bytes / ms_copy / 1e6, "parts": len(pipe.parts),
+                             "what": "decode in parts; each part's token range is copied into GPU 0's blob "
+                                     "(cudaMemcpy2DAsync over NVLink, second stream) while the next part is decoded"}
+    res["delivered_bits_equal"] = same and ok_status
+    res["tokens_per_s"] = T / min(ms_copy, ms_nccl) * 1e3
+    return res
+
+
 def run_ours(args, spec):
     import torch
     import torch.distributed as dist
 
     from cachegen_b200 import _lib
-    from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
-    from cachegen_b200.serde import CacheGenDeserializer, CacheGenSerializer
+    from cachegen_b200.serde import CacheGenSerializer
     from cachegen_b200.serde.cachegen_basics import CacheGenGPUBytestream, CacheGenGPUEncoderOutput
-    from cachegen_b200.parallel import PipelinedDelivery, buffer_on_root, gather_layers, max_over_ranks, partition
+    from cachegen_b200.parallel import PipelinedDelivery, buffer_on_root, gather_layers, partition
     from cachegen_b200.serde.cachegen_basics import CacheGenConfig
     from cachegen_b200.synth import generate_kv
 
@@ -265,11 +600,11 @@ def run_ours(args, spec):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    h = Harness(dev, rank, world)
+    barrier, timed = h.barrier, h.timed
 
     L_total, H, D, T = spec["num_layers"], spec["num_heads"], spec["head_size"], spec["num_tokens"]
     C = H * D
-    config = LMCacheEngineConfig.from_defaults(chunk_size=CHUNK_TOKENS)
-    meta = LMCacheEngineMetadata(model_name=spec["model_name"], world_size=world, worker_id=rank, fmt="vllm")
     by_layers = args.shard == "layers" and world > 1
     full_cfg = CacheGenConfig.from_model_name(spec["model_name"])
     if by_layers:
@@ -279,8 +614,7 @@ def run_ours(args, spec):
         cfg, L, first_layer, seed = full_cfg.layer_slice(mine.start, mine.stop), len(mine), mine.start, spec["seed"]
     else:
         cfg, L, first_layer, seed = full_cfg, L_total, 0, spec["seed"] + 1000 * rank
-    ser = CacheGenSerializer(config, meta, cachegen_config=cfg, table_max_bins=full_cfg.max_bins)
-    de = CacheGenDeserializer(config, meta, cachegen_config=cfg, out_dtype=torch.float16)
+    ser, de, config, meta = make_serde(spec, world, rank, cachegen_config=cfg, table_max_bins=full_cfg.max_bins)
 
     # ---- set-up (untimed): this rank's share, encoded chunk by chunk as LMCacheEngine.store would
     kv = generate_kv(L, H, D, T, seed, key_rho=spec["key_rho"], device=dev, dtype=torch.float16, first_layer=first_layer)
@@ -294,8 +628,10 @@ def run_ours(args, spec):
         enc1.record()
         torch.cuda.synchronize()
         ms_encode = enc0.elapsed_time(enc1)
+    kv_chunk0 = kv[:, :, :CHUNK_TOKENS].clone()
     out = torch.empty((L, 2, T, H, D), dtype=torch.float16, device=dev)
     plan = de.plan(chunks, out=out)
+    launches_per_step = plan.launches
     kv_bytes = 2 * L * C * T * 2
     payload = plan.payload_bytes
     per_token = {"payload": payload / T, "tables": plan.table_bytes / T, "lengths": plan.length_bytes / T,
@@ -303,7 +639,8 @@ def run_ours(args, spec):
     per_token["total"] = sum(per_token.values())
     algorithmic = plan.output_bytes + payload + plan.table_bytes + plan.length_bytes + plan.scale_bytes
 
-    # correctness gate before timing: decoded values within the quantiser's error bound
+    # sanity gate before timing: decoded values within the quantiser's error bound (bit equality with the
+    # reference's results is what the GPU tests check, not this)
     plan.run()
     de.check_status()
     step = torch.cat((chunks[0].max_tensors_key, chunks[0].max_tensors_value)).float().reshape(2 * L, -1, 1)
@@ -313,23 +650,6 @@ def run_ours(args, spec):
     bound = 0.5 * step / cq[:, None, None] * 1.001 + step * 2.0 ** -10 + 1e-6
     assert bool(((got - ref).abs() <= bound).all()), "decoded KV violates the quantiser's error bound"
     del got, ref
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps, warmup):
-        for _ in range(warmup):
-            fn()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        return max_over_ranks(e0.elapsed_time(e1), device=dev) / steps
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -419,11 +739,20 @@ def run_ours(args, spec):
             "lengths": flat_plan.length_bytes / T, "scales": flat_plan.scale_bytes / T,
             "container": sum(c.header.total for c in flat_gpu) / T}
         flat_host = [c.pin_memory() for c in flat_gpu]
-        kv_chunk0 = kv[:, :, :CHUNK_TOKENS].clone()
-        del flat_plan, flat_gpu, kv
+        del flat_plan, flat_gpu
+        kv = None
         e2e = measure_host(flat_host, sum(c.header.total for c in flat_host),
                            "CacheGenDeserializer.decode_many_host on CGB2 containers (CacheGenSerializer.encode_flat) "
                            "held in pinned host memory; 16 groups, copies of one group overlap the decode of the previous")
+        # the same copies with no decode: what the bus alone takes (every rank copies at once)
+        dev_flat = [torch.empty_like(c.blob, device=dev) for c in flat_host]
+
+        def copy_only():
+            for d_, c in zip(dev_flat, flat_host):
+                d_.copy_(c.blob, non_blocking=True)
+        extra["h2d_only_ms"] = timed(copy_only, max(2, args.steps // 2), 2)
+        extra["h2d_only_gbps_per_gpu"] = sum(c.header.total for c in flat_host) / extra["h2d_only_ms"] / 1e6
+        del dev_flat
         del flat_host
         # (2) the reference's blob layout (tensors of CacheGenGPUEncoderOutput), same call
         host_chunks = [CacheGenGPUEncoderOutput(
@@ -493,6 +822,22 @@ def run_ours(args, spec):
                 "what": f"one {one.shape[2]}-token chunk at QUANT_LEVEL 1, 2 and 3: CacheGenSerializer.encode_levels "
                         "against three CacheGenSerializer.encode calls"}
 
+    # ---- legs beside the headline
+    if not args.no_extra and not by_layers:
+        chunk0 = chunks[0]
+        kv = plan = out = None
+        if world == 1:
+            extra["reference_cuda_ext"] = leg_reference_cuda_ext(h, ser, de, kv_chunk0, chunk0)
+            del chunks
+            torch.cuda.empty_cache()
+            extra["config3"] = leg_config3(h, args)
+            torch.cuda.empty_cache()
+            extra["config5"] = leg_config5(h, args)
+        else:
+            del chunks
+            torch.cuda.empty_cache()
+            extra["delivered_kv"] = leg_delivered_kv(h, args)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -510,18 +855,16 @@ def run_ours(args, spec):
         "tokens_per_s": (T if by_layers else world * T) / ms_step * 1e3,
         "bytes_per_token": per_token,
         "kv_bytes_per_token": kv_bytes / T,
-        "gpu_launches": plan.launches * args.steps,
-        "launches_per_step": plan.launches,
+        "gpu_launches": launches_per_step * args.steps,
+        "launches_per_step": launches_per_step,
         "kernel_ms": {"decode_dequant": ms_kernel, "offsets": ms_offsets},
         "encode": {"value": kv_bytes / ms_encode / 1e6, "unit": "GB/s", "ms": ms_encode,
                    "what": "CacheGenSerializer.encode_many: every chunk of the cache, one host sync per 16 chunks, "
                            "KV resident in HBM, second pass of set-up"},
-        "roofline": {"bound": "hbm", "kernel": "decode_dequant_kernel", "achieved": achieved, "peak": peak,
-                     "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": (NCU_TRAFFIC_BYTES_PER_TOKEN[(L, H, D)] * T
-                                 if (L, H, D) in NCU_TRAFFIC_BYTES_PER_TOKEN else None),
-                     "traffic_source": "ncu capture of a 2,048-token launch scaled by tokens",
-                     "algorithmic_bytes_per_launch": algorithmic},
+        "roofline": dict({"bound": "hbm", "kernel": "decode_dequant_multi_kernel", "achieved": achieved, "peak": peak,
+                          "peak_kind": peak_kind, "unit": "GB/s", "frac": achieved / peak,
+                          "frac_of_write_roofline": total_kv_bytes / world / ms_kernel / 1e6 / peak if not by_layers else None,
+                          "algorithmic_bytes_per_launch": algorithmic, "traffic": None}, **ncu_counters(L, H, D, T)),
         "clocks": clocks,
     }
     if e2e:

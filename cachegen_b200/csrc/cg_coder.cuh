@@ -422,11 +422,27 @@ CG_HD void decode_streams(Smem sm, const uint32_t (&col)[NS], uint32_t det, int 
         for (int i = 0; i < NS; ++i) {
             const bool t1 = cg_umulhi(st[i].span32, r_mid[i]) <= st[i].offset;
             uint32_t x = t1 ? col_top[i] : col[i];
-            x = cg_umulhi(st[i].span32, t1 ? r_hi[i] : r_lo[i]) <= st[i].offset ? x + kHalf : x;
-            a[i] = FastSearch<FL - 3>::run(sm, x, st[i].span32, st[i].offset);
+            a[i] = cg_umulhi(st[i].span32, t1 ? r_hi[i] : r_lo[i]) <= st[i].offset ? x + kHalf : x;
+        }
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+        for (int i = 0; i < NS; ++i) a[i] = FastSearch<FL - 3>::run(sm, a[i], st[i].span32, st[i].offset);
+        uint32_t e0[NS], e1[NS];
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+        for (int i = 0; i < NS; ++i) {
+            e0[i] = sm.ld(a[i]);
+            e1[i] = sm.ld(a[i] + kTableRowBytes);
+        }
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+        for (int i = 0; i < NS; ++i) {
             rare = rare || a[i] >= det || bw[i].short_of_bits();
-            flo[i] = cg_umulhi(st[i].span32, sm.ld(a[i]));
-            fhi[i] = cg_umulhi(st[i].span32, sm.ld(a[i] + kTableRowBytes));
+            flo[i] = cg_umulhi(st[i].span32, e0[i]);
+            fhi[i] = cg_umulhi(st[i].span32, e1[i]);
         }
         if (cg_any_lane(lanes, rare)) {
             bool low = false, odd = false;
