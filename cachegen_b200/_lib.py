@@ -41,8 +41,14 @@ class DecodeJob(ctypes.Structure):
     ]
 
 
+class WorkspaceSizes(ctypes.Structure):
+    """cg_workspace_sizes"""
+    _fields_ = [(n, ctypes.c_int64) for n in ("nsub", "scratch_stride", "encode_scratch", "encode_lengths",
+                                              "encode_group_off", "encode_sub_off", "decode_group_off", "symbols")]
+
+
 EXPORTS = [
-    "cg_version", "cg_status_string", "cg_last_cuda_error",
+    "cg_version", "cg_status_string", "cg_last_cuda_error", "cg_workspace_bytes",
     "cg_calculate_cdf", "cg_encode_padded", "cg_decode_padded", "cg_decode_prefsum", "cg_decode_prefsum_warp",
     "cg_quantize_cdf", "cg_row_absmax", "cg_quantize_cdf_scaled", "cg_pack_sparse_tables", "cg_encode_chunk", "cg_compact_streams",
     "cg_decode_offsets", "cg_decode_dequant", "cg_decode_dequant_static",
@@ -72,6 +78,7 @@ def lib():
     L.cg_status_string.restype = ctypes.c_char_p
     L.cg_status_string.argtypes = [i]
     L.cg_last_cuda_error.restype = ctypes.c_char_p
+    L.cg_workspace_bytes.argtypes = [i, i, i, ctypes.POINTER(WorkspaceSizes)]
     L.cg_calculate_cdf.argtypes = [p, S3, i, i, i, i, p, p]
     L.cg_encode_padded.argtypes = [p, p, S3, i, i, i, i, p, i64, p, p, p]
     L.cg_decode_padded.argtypes = [p, p, i64, p, p, S3, i, i, i, i, p, p]
@@ -92,6 +99,13 @@ def lib():
             fn.restype = i
     _lib = L
     return L
+
+
+def workspace_sizes(nrows, ntokens, nchannels) -> WorkspaceSizes:
+    """cg_workspace_bytes: sizes of the caller-allocated buffers of the fused calls for one chunk."""
+    out = WorkspaceSizes()
+    check(lib().cg_workspace_bytes(int(nrows), int(ntokens), int(nchannels), ctypes.byref(out)), "cg_workspace_bytes")
+    return out
 
 
 def strides3(t):

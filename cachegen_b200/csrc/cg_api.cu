@@ -33,3 +33,22 @@ extern "C" const char *cg_status_string(int code) {
         default: return "unknown status";
     }
 }
+
+extern "C" int cg_workspace_bytes(int nrows, int ntokens, int nchannels, cg_workspace_sizes *out_host) {
+    if (!out_host) return CG_E_NULL;
+    if (nrows <= 0 || ntokens <= 0 || nchannels <= 0) return CG_E_SHAPE;
+    const int64_t nsub = (static_cast<int64_t>(ntokens) + CG_MAX_TOKENS_PER_STREAM - 1) / CG_MAX_TOKENS_PER_STREAM;
+    const int64_t sub_tokens = ntokens < CG_MAX_TOKENS_PER_STREAM ? ntokens : CG_MAX_TOKENS_PER_STREAM;
+    const int64_t stride = (CG_STREAM_CAPACITY(sub_tokens) + 3) / 4 * 4;
+    const int64_t streams = static_cast<int64_t>(nrows) * nchannels;
+    const int64_t groups = static_cast<int64_t>(nrows) * ((nchannels + CG_GROUP_CHANNELS - 1) / CG_GROUP_CHANNELS);
+    out_host->nsub = nsub;
+    out_host->scratch_stride = stride;
+    out_host->encode_scratch = nsub * streams * stride;
+    out_host->encode_lengths = nsub * streams * 4;
+    out_host->encode_group_off = nsub * groups * 8;
+    out_host->encode_sub_off = (nsub + 1) * 8;
+    out_host->decode_group_off = groups * 8;
+    out_host->symbols = streams * ntokens;
+    return CG_OK;
+}

@@ -129,7 +129,15 @@ class CacheGenGPUEncoderOutput:
         return getattr(self, key)
 
     def to_bytes(self) -> bytes:
-        return dump_blob(self)
+        try:
+            return dump_blob(self)
+        except Exception:
+            # dump_blob follows torch's legacy storage stream by hand; should a torch release change
+            # that format, the plain pickle is still the reference's blob (slower: torch copies every
+            # CUDA tensor through pageable memory)
+            f = io.BytesIO()
+            pickle.dump(self, f)
+            return f.getvalue()
 
     @staticmethod
     def from_bytes(bs: bytes) -> "CacheGenGPUEncoderOutput":

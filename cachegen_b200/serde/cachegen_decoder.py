@@ -14,6 +14,7 @@ import torch
 from .. import _lib
 from .. import torchac_cuda
 from ..config import LMCacheEngineConfig, LMCacheEngineMetadata
+from ..utils import _lmcache_nvtx_annotate
 from . import cachegen_basics as CGBasics
 from . import flat_format
 from .cachegen_basics import CacheGenConfig, CacheGenGPUBytestream, CacheGenGPUEncoderOutput
@@ -36,6 +37,7 @@ def do_dequantize(t: torch.Tensor, bins: torch.Tensor, maxtensors: torch.Tensor)
     return t
 
 
+@_lmcache_nvtx_annotate
 def bytes_to_tensor(bs: bytes, device="cuda") -> torch.Tensor:
     """A byte string as a uint8 tensor on `device` (dec.py:37-41); to a GPU through pinned staging."""
     import warnings
@@ -49,6 +51,7 @@ def bytes_to_tensor(bs: bytes, device="cuda") -> torch.Tensor:
     return view.clone()
 
 
+@_lmcache_nvtx_annotate
 def recombine_bytes(bytes_tensor: torch.Tensor, output_lengths: torch.Tensor) -> torch.Tensor:
     """Back-to-back streams as padded rows [nlayers, nchannels, 256] for decode_fast_new
     (dec.py:43-49): row (r, c) holds the 256 bytes that start where stream (r, c) starts, reading
@@ -61,6 +64,7 @@ def recombine_bytes(bytes_tensor: torch.Tensor, output_lengths: torch.Tensor) ->
     return bytes_tensor[index].reshape(*output_lengths.shape, width)
 
 
+@_lmcache_nvtx_annotate
 def decode_chunk(cdf: torch.Tensor, data_chunk: CacheGenGPUBytestream, target_buffer: torch.Tensor) -> None:
     """Symbols of one sub-chunk into target_buffer [2L, ntokens, C] uint8, strided ok (dec.py:53-75)."""
     lengths = data_chunk.bytestream_lengths
@@ -68,6 +72,7 @@ def decode_chunk(cdf: torch.Tensor, data_chunk: CacheGenGPUBytestream, target_bu
     torchac_cuda.decode_fast_prefsum(cdf, data_chunk.bytestream, length_prefsum, target_buffer)
 
 
+@_lmcache_nvtx_annotate
 def decode_function_gpu(cdf: torch.Tensor, data_chunks: List[CacheGenGPUBytestream], layers_in_key: int,
                         chunk_size: int, output: torch.Tensor):
     """Symbol-level decode with the reference's signature (dec.py:78-112): fills `output`
@@ -517,6 +522,7 @@ class CacheGenDeserializer(Deserializer):
                   for b in blobs]
         return self.decode_many(chunks, out=out)
 
+    @_lmcache_nvtx_annotate
     def from_bytes(self, bs: bytes) -> torch.Tensor:
         if flat_format.is_flat(bs):
             # a CGB2 container: one copy to the GPU, decoded in place

@@ -21,6 +21,7 @@ import torch
 
 from .. import _lib
 from ..config import LMCacheEngineConfig, LMCacheEngineMetadata
+from ..utils import _lmcache_nvtx_annotate
 from . import cachegen_basics as CGBasics
 from . import flat_format
 from .cachegen_basics import CacheGenConfig, CacheGenGPUBytestream, CacheGenGPUEncoderOutput
@@ -43,6 +44,7 @@ def _split_kv(tensor: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return torch.unbind(tensor.reshape(num_layers, 2, num_tokens, num_heads * head_size), dim=1)
 
 
+@_lmcache_nvtx_annotate
 def torch_quant_vectorized(bins: torch.Tensor, input_groups: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """The reference's quantiser with its own signature (enc.py:42-59), on the quantise kernel: bins
     [R] (any numeric type), input_groups [R, T, C] float16 / bfloat16 on the GPU -> (symbols int8
@@ -72,11 +74,13 @@ def torch_quant_vectorized(bins: torch.Tensor, input_groups: torch.Tensor) -> Tu
     return sym[:R], scales[:R].unsqueeze(-1)
 
 
+@_lmcache_nvtx_annotate
 def concat_max(max1) -> torch.Tensor:
     """A sequence of per-layer max tensors as one tensor with a leading layer axis (enc.py:62-70)."""
     return torch.stack([max1[i] for i in range(len(max1))])
 
 
+@_lmcache_nvtx_annotate
 def collect_bytes(output_buffer: torch.Tensor, output_lengths: torch.Tensor) -> torch.Tensor:
     """The first output_lengths[r, c] bytes of every row output_buffer[r, c, :], back to back in
     (r, c) order, as one uint8 tensor (enc.py:210-222), on the offset and compaction kernels."""
@@ -109,6 +113,7 @@ def collect_bytes(output_buffer: torch.Tensor, output_lengths: torch.Tensor) -> 
     return out
 
 
+@_lmcache_nvtx_annotate
 def encode_ntokens(cdf_int: torch.Tensor, encode_input: torch.Tensor, output_buffer: torch.Tensor,
                    output_lengths: torch.Tensor) -> torch.Tensor:
     """encode_fast_new into the caller's buffers, then collect_bytes (enc.py:225-242)."""
@@ -345,6 +350,7 @@ def encode_levels(kv: torch.Tensor, levels: list) -> list:
     return out
 
 
+@_lmcache_nvtx_annotate
 def encode_function(kv: torch.Tensor, config: CacheGenConfig, key_bins: torch.Tensor, value_bins: torch.Tensor,
                     chunk_size: int, max_bins: int = None) -> CacheGenGPUEncoderOutput:
     """Encodes one chunk of KV, [L, 2, T, H, D] on the GPU, T == chunk_size (enc.py:247-301)."""
@@ -424,7 +430,8 @@ def encode_flat(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tens
         kind, tables = flat_format.TABLES_CDF, cdf.view(torch.uint8).reshape(-1)
     header = flat_format.layout(L, H, D, T, kmax + 1, kv.dtype, kind, tables.numel(), flat_format.LENGTHS_U16, offs,
                                 bins_checksum=flat_format.bins_checksum(bins_cpu))
-    blob = torch.empty(header.total, dtype=torch.uint8, device=kv.device)
+    # zeroed, so that the alignment gaps between the sections are defined: the same KV gives the same bytes
+    blob = torch.zeros(header.total, dtype=torch.uint8, device=kv.device)
     head = header.pack()
     blob[:len(head)].copy_(torch.frombuffer(bytearray(head), dtype=torch.uint8), non_blocking=True)
     chunk = flat_format.FlatChunk(blob, header)
@@ -500,6 +507,7 @@ class CacheGenSerializer(Serializer):
             tensor = tensor.contiguous()
         return encode_flat(tensor, self.key_bins, self.value_bins, compact_tables, max_bins=self.table_max_bins)
 
+    @_lmcache_nvtx_annotate
     def to_bytes(self, tensor: torch.Tensor) -> bytes:
         """KV blob ([L,2,T,H,D] for "vllm", [L,2,H,T,D] for "huggingface") -> bytes (enc.py:324-348):
         the reference's pickle, or a CGB2 container when wire_format == "flat"."""

@@ -74,6 +74,9 @@ def encode_fast_new(cdf: torch.Tensor, input_sym: torch.Tensor, output_buffer: t
     _check(input_sym.is_cuda, "Input symbols should be on GPU")
     _check(output_buffer.is_cuda, "Output buffer should be on GPU")
     _check(output_lengths.is_cuda, "Output lengths should be on GPU")
+    _check(cdf.dim() == 3 and input_sym.dim() == 3 and output_buffer.dim() == 3 and output_lengths.dim() == 2,
+           "expected cdf, input symbols and output buffer of rank 3 and output lengths of rank 2")
+    _check(input_sym.dtype in (torch.int8, torch.uint8), "expected int8 input symbols")
     cs, ins, os_, ls = cdf.shape, input_sym.shape, output_buffer.shape, output_lengths.shape
     _check(cs[0] == ins[0], "CDF and input should have the same number of layers")
     _check(cs[1] == ins[2], "CDF and input should have the same number of layers")
@@ -116,6 +119,9 @@ def decode_fast_new(cdf: torch.Tensor, bytestreams: torch.Tensor, lengths: torch
     _check(bytestreams.is_cuda, "Bytestreams should be on GPU")
     _check(lengths.is_cuda, "Lengths should be on GPU")
     _check(output.is_cuda, "Output should be on GPU")
+    _check(cdf.dim() == 3 and bytestreams.dim() == 3 and lengths.dim() == 2 and output.dim() == 3,
+           "expected cdf, bytestreams and output of rank 3 and lengths of rank 2")
+    _check(bytestreams.dtype == torch.uint8 and output.dtype == torch.uint8, "expected uint8 bytestreams and output")
     cs, bs, ls, os_ = cdf.shape, bytestreams.shape, lengths.shape, output.shape
     _check(cs[0] == bs[0], "CDF and bytestreams should have the same number of layers")
     _check(cs[1] == bs[1], "CDF and bytestreams should have the same number of channels")
@@ -143,6 +149,9 @@ def _decode_prefsum(entry: str, cdf, bytestreams, lengths_prefsum, output) -> No
     _check(bytestreams.is_cuda, "Bytestreams should be on GPU")
     _check(lengths_prefsum.is_cuda, "Lengths should be on GPU")
     _check(output.is_cuda, "Output should be on GPU")
+    _check(cdf.dim() == 3 and lengths_prefsum.dim() == 2 and output.dim() == 3,
+           "expected cdf and output of rank 3 and prefix sums of rank 2")
+    _check(bytestreams.dtype == torch.uint8 and output.dtype == torch.uint8, "expected uint8 bytestreams and output")
     cs, ls, os_ = cdf.shape, lengths_prefsum.shape, output.shape
     _check(cs[0] == ls[0], "CDF and lengths should have the same number of layers")
     _check(cs[1] == ls[1], "CDF and lengths should have the same number of channels")

@@ -93,6 +93,24 @@ extern "C" {
 #define CG_S_COUNT_OVERFLOW 8  /* a histogram count above 255: the byte-count tables are not usable */
 #define CG_S_BAD_TABLE 16     /* CG_TABLES_SPARSE offsets reach past the table set (read as zero counts) */
 
+/*
+ * Sizes in bytes of the buffers a caller allocates for the fused calls, for one chunk of
+ * `ntokens` tokens with `nrows` = 2L rows of `nchannels` channels (no counterpart in the reference,
+ * whose torch ops allocate as they go).  Returns CG_E_SHAPE for non-positive extents.
+ */
+typedef struct cg_workspace_sizes {
+    int64_t nsub;              /* sub-chunks of the chunk: ceil(ntokens / 256) */
+    int64_t scratch_stride;    /* bytes per stream in the encoder's scratch: CG_STREAM_CAPACITY, rounded to 4 */
+    int64_t encode_scratch;    /* cg_encode_chunk scratch:        nsub * nrows * nchannels * scratch_stride */
+    int64_t encode_lengths;    /* cg_encode_chunk lengths_out:    nsub * nrows * nchannels * 4 */
+    int64_t encode_group_off;  /* cg_encode_chunk group_off_out:  nsub * nrows * ceil(nchannels/128) * 8 */
+    int64_t encode_sub_off;    /* cg_encode_chunk sub_off_out:    (nsub + 1) * 8 */
+    int64_t decode_group_off;  /* cg_decode_offsets group_off_out, per job (= per sub-chunk):
+                                  nrows * ceil(nchannels/128) * 8 */
+    int64_t symbols;           /* cg_quantize_cdf sym_out:        nrows * ntokens * nchannels */
+} cg_workspace_sizes;
+int cg_workspace_bytes(int nrows, int ntokens, int nchannels, cg_workspace_sizes *out_host);
+
 const char *cg_version(void);
 const char *cg_status_string(int code);
 /* text of the last CUDA runtime error seen by this library on the calling thread */

@@ -230,3 +230,59 @@ def test_a_c_program_links_against_the_header_and_the_library(tmp_path):
     assert run.returncode == 0, run.stdout + run.stderr
     assert "all checks passed" in run.stdout
     assert ctypes.sizeof(_lib.DecodeJob) == 96   # the ctypes mirror has the size the C program checked
+
+
+def test_workspace_sizes_match_what_the_encoder_allocates():
+    """cg_workspace_bytes against the sizes the Python host side works out for itself."""
+    from cachegen_b200 import _lib
+    ws = _lib.workspace_sizes(64, 700, 4096)
+    assert ws.nsub == 3 and ws.scratch_stride == _lib.stream_capacity(256)
+    assert ws.encode_scratch == 3 * 64 * 4096 * 520 and ws.encode_lengths == 3 * 64 * 4096 * 4
+    assert ws.encode_group_off == 3 * 64 * 32 * 8 and ws.encode_sub_off == 4 * 8
+    assert ws.decode_group_off == 64 * 32 * 8 and ws.symbols == 64 * 700 * 4096
+    short = _lib.workspace_sizes(2, 10, 130)
+    assert short.scratch_stride == 28 and short.decode_group_off == 2 * 2 * 8
+    import pytest
+    with pytest.raises(RuntimeError):
+        _lib.workspace_sizes(0, 10, 130)
+
+
+def test_nvtx_decorator_is_a_no_op_without_the_package(monkeypatch):
+    import builtins
+    import sys
+    from cachegen_b200.utils import _get_color_for_nvtx, _lmcache_nvtx_annotate
+    real_import = builtins.__import__
+
+    def no_nvtx(name, *a, **k):
+        if name == "nvtx":
+            raise ImportError(name)
+        return real_import(name, *a, **k)
+    monkeypatch.delitem(sys.modules, "nvtx", raising=False)
+    monkeypatch.setattr(builtins, "__import__", no_nvtx)
+
+    def f(x):
+        return x + 1
+    assert _lmcache_nvtx_annotate(f) is f and f(1) == 2
+    assert _get_color_for_nvtx("decode_chunk") in ("green", "blue", "purple", "rapids")
+
+
+def test_blob_writer_falls_back_to_plain_pickle(monkeypatch):
+    """to_bytes must still give the reference's blob when the hand-built storage streams cannot be
+    made (a torch release that changes the legacy format)."""
+    import io
+    import pickle
+    import torch
+    from cachegen_b200.serde import cachegen_basics as B
+    o = B.CacheGenGPUEncoderOutput(
+        [B.CacheGenGPUBytestream(torch.arange(100).to(torch.uint8), torch.ones(2, 4, dtype=torch.int32), 5)],
+        torch.zeros((2, 4, 9), dtype=torch.int16), torch.ones(1, 5, 1).half(), torch.ones(1, 5, 1).half(), 1, 4)
+    f = io.BytesIO()
+    pickle.dump(o, f)
+
+    def broken(*a, **k):
+        raise AttributeError("storage stream layout changed")
+    monkeypatch.setattr(B, "dump_blob", broken)
+    blob = o.to_bytes()
+    assert blob == f.getvalue()
+    back = B.CacheGenGPUEncoderOutput.from_bytes(blob)
+    assert torch.equal(back.cdf, o.cdf) and back.data_chunks[0].ntokens == 5

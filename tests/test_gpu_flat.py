@@ -199,3 +199,19 @@ def test_corrupt_sparse_offsets_are_flagged_not_followed():
     assert out.shape == good.shape
     assert torch.equal(out[:2, 0], good[:2, 0])  # rows 0 and 1 (groups 0..3) are untouched by the damage
     assert torch.equal(de.decode(chunk), good)
+
+
+def test_the_same_kv_gives_the_same_container_bytes():
+    """The alignment gaps of a container are zeroed: two encodes of one chunk agree byte for byte, whatever
+    the allocator handed out (stored chunks can be hashed and de-duplicated)."""
+    from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
+    from cachegen_b200.serde import CacheGenSerializer
+    from cachegen_b200.synth import generate_kv
+    kv = generate_kv(32, 2, 128, 200, seed=5, device="cuda", dtype=torch.float16)
+    ser = CacheGenSerializer(LMCacheEngineConfig.from_defaults(chunk_size=256),
+                             LMCacheEngineMetadata(model_name="lmsys/longchat-7b-16k", world_size=1, worker_id=0, fmt="vllm"))
+    first = ser.encode_flat(kv).tobytes()
+    junk = torch.full((64 << 20,), 0xAB, dtype=torch.uint8, device="cuda")  # dirty the allocator's free blocks
+    del junk
+    second = ser.encode_flat(kv).tobytes()
+    assert first == second

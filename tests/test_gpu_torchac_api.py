@@ -175,6 +175,15 @@ def test_argument_checks_raise_like_the_reference(tc):
     pref = torch.zeros((2, 128), dtype=torch.int64, device="cuda")
     with pytest.raises(RuntimeError, match="Number of tokens"):
         tc.decode_fast_prefsum(cdf, torch.zeros(8, dtype=torch.uint8, device="cuda"), pref, out)
+    # element types the reference's accessors reject too: the kernels address bytes
+    with pytest.raises(RuntimeError, match="int8 input symbols"):
+        tc.encode_fast_new(cdf, sym[:, :16].to(torch.int32), buf, lens)
+    with pytest.raises(RuntimeError, match="uint8 bytestreams and output"):
+        tc.decode_fast_prefsum(cdf, torch.zeros(8, dtype=torch.uint8, device="cuda"), pref, out[:, :16].to(torch.int32))
+    with pytest.raises(RuntimeError, match="uint8 bytestreams and output"):
+        tc.decode_fast_new(cdf, buf.to(torch.int16), lens, out[:, :16])
+    with pytest.raises(RuntimeError, match="rank"):
+        tc.decode_fast_new(cdf, buf.reshape(2, -1), lens, out[:, :16])
 
 
 @pytest.mark.parametrize("max_bins,T,C", [(32, 256, 320), (16, 77, 37), (8, 1, 128), (12, 200, 130)])
