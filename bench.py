@@ -525,6 +525,40 @@ def leg_config5(h, args):
                     "lengths and scales"}
 
 
+def leg_anchor_delta(h, spec, kv_part):
+    """Anchor-token delta coding (no counterpart in the reference) on the first tokens of the workload:
+    key rows in groups of 4 with half the bins on the residual tokens, against the plain codec."""
+    torch = h.torch
+    from cachegen_b200.serde import DeltaCoding
+    L, _, T, H, D = kv_part.shape
+    res = {"tokens": T, "settings": "groups of 4, residual bins = bins // 2, key rows only"}
+    for name, delta in (("plain", None), ("delta", DeltaCoding(4, 2, "keys"))):
+        import cachegen_b200.serde as S
+        from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
+        config = LMCacheEngineConfig.from_defaults(chunk_size=CHUNK_TOKENS)
+        meta = LMCacheEngineMetadata(model_name=spec["model_name"], world_size=1, worker_id=0, fmt="vllm")
+        ser = S.CacheGenSerializer(config, meta, delta=delta)
+        de = S.CacheGenDeserializer(config, meta, out_dtype=torch.float16, delta=delta)
+        box = {}
+
+        def encode():
+            box["chunks"] = ser.encode_many(kv_part, CHUNK_TOKENS, batch=16)
+        encode()
+        ms_enc = h.timed(encode, 3, 1, local=True)
+        out = torch.empty((L, 2, T, H, D), dtype=torch.float16, device=h.dev)
+        plan = de.plan(box["chunks"], out=out, workspace={})
+        ms_dec = h.timed(plan.run, 5, 2, local=True)
+        de.check_status()
+        kv_bytes = kv_part.numel() * 2
+        err = (out.float() - kv_part.float())
+        res[name] = {"payload_bytes_per_token": plan.payload_bytes / T, "encode_gbps": kv_bytes / ms_enc / 1e6,
+                     "decode_gbps": kv_bytes / ms_dec / 1e6,
+                     "key_mse": float((err[:, 0] ** 2).mean()), "value_mse": float((err[:, 1] ** 2).mean())}
+        del out, plan, box
+    res["payload_ratio"] = res["delta"]["payload_bytes_per_token"] / res["plain"]["payload_bytes_per_token"]
+    return res
+
+
 def leg_delivered_kv(h, args):
     """BASELINE config 4 in the process group of the --gpus N run: the Llama-70B-shape cache (80 layers x 8
     KV heads x 128, 16,384 tokens) sharded by layers, every rank decodes its layers and the decoded KV is
@@ -829,6 +863,10 @@ def run_ours(args, spec):
         if world == 1:
             extra["reference_cuda_ext"] = leg_reference_cuda_ext(h, ser, de, kv_chunk0, chunk0)
             del chunks
+            torch.cuda.empty_cache()
+            extra["anchor_delta"] = leg_anchor_delta(h, spec, generate_kv(L, H, D, 4 * CHUNK_TOKENS, spec["seed"],
+                                                                       key_rho=spec["key_rho"], device=dev,
+                                                                       dtype=torch.float16))
             torch.cuda.empty_cache()
             extra["config3"] = leg_config3(h, args)
             torch.cuda.empty_cache()

@@ -52,6 +52,7 @@ EXPORTS = [
     "cg_calculate_cdf", "cg_encode_padded", "cg_decode_padded", "cg_decode_prefsum", "cg_decode_prefsum_warp",
     "cg_quantize_cdf", "cg_row_absmax", "cg_quantize_cdf_scaled", "cg_pack_sparse_tables", "cg_encode_chunk", "cg_compact_streams",
     "cg_decode_offsets", "cg_decode_dequant", "cg_decode_dequant_static",
+    "cg_quantize_cdf_delta", "cg_decode_dequant_delta",
 ]
 CG_STATIC_OFFSET_ENTRIES = 131072
 
@@ -93,6 +94,8 @@ def lib():
     L.cg_decode_offsets.argtypes = [ctypes.POINTER(DecodeJob), i, i, i, p, p, p]
     L.cg_decode_dequant.argtypes = [ctypes.POINTER(DecodeJob), i, i, i, i, i, p, i, i, i64, i64, i64, i64, p, p]
     L.cg_decode_dequant_static.argtypes = L.cg_decode_dequant.argtypes
+    L.cg_quantize_cdf_delta.argtypes = [p, i, i64, i64, i64, i64, i, i, i, i, p, i, i, p, p, p, p, p, p, p, p]
+    L.cg_decode_dequant_delta.argtypes = [ctypes.POINTER(DecodeJob), i, i, i, i, i, p, i, p, i, i, i64, i64, i64, i64, p, p]
     for name in EXPORTS:
         fn = getattr(L, name)
         if name not in ("cg_version", "cg_status_string", "cg_last_cuda_error"):

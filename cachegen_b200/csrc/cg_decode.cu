@@ -114,6 +114,8 @@ __global__ void __launch_bounds__(kGroup) decode_symbols_warp_kernel(const SymDe
 // ---- fused decode + dequantise + KV-layout store --------------------------------------------------------
 struct FusedDecodeParams {
     int njobs, nlayers, nheads, head_size, nchannels, lp, nslab;
+    int delta_group;         // 0: every token is coded on its own (the reference's behaviour)
+    const float *res_bins;   // anchor-token delta: residual bin count per row, <= 0 for rows without it
     const float *bins;
     int64_t o_layer, o_kv, o_token, o_head;
     int32_t *status;
@@ -249,14 +251,17 @@ __device__ __forceinline__ uint32_t pack_pair<CG_BF16>(float v0, float v1) {
 // more leaves the compiler 80 registers a thread, which it needs to interleave the NS chains.
 constexpr int kMultiBlocksPerSM = 12;
 
-template <int NS, int OUT_DT>
+// DELTA (anchor-token delta, see cg_decode_dequant_delta): in rows with residual bins every token that is
+// not the first of its group of delta_group adds its value, ((sym - Cq_a) / Cq_r) * max, to its
+// anchor's value as the KV dtype holds it; the sum is cast to the output type.
+template <int NS, int OUT_DT, bool DELTA>
 __global__ void __launch_bounds__(kGroup / NS, kMultiBlocksPerSM)
 decode_dequant_multi_kernel(const __grid_constant__ FusedDecodeParams p, int scale_dt, int full_levels) {
     constexpr int kThreads = kGroup / NS;
     constexpr int kWarps = kThreads / 32;
     extern __shared__ uint32_t smem[];
     __shared__ float scale_f[kSubTokens];
-    __shared__ float lut[CG_MAX_LP];
+    __shared__ float lut[(DELTA ? 2 : 1) * CG_MAX_LP];  // DELTA: the residual tokens' table follows the anchors'
     __shared__ int warp_sums[kWarps];
 
     const cg_decode_job &job = p.jobs[blockIdx.z];
@@ -303,6 +308,23 @@ decode_dequant_multi_kernel(const __grid_constant__ FusedDecodeParams p, int sca
     for (int t = tid; t < ntok; t += kThreads) scale_f[t] = half_bits_to_float(__ldg(sc + t), scale_dt);
     const float cqf = half_range(__ldg(p.bins + row));
     for (int m = tid; m < p.lp - 1; m += kThreads) lut[m] = __fdiv_rn(__fsub_rn(static_cast<float>(m), cqf), cqf);
+    uint32_t group_mask = 0xFFFFFFFFu;  // token index & group_mask == 0: an anchor (every token without delta)
+    if (DELTA) {
+        float cqr = 0.0f;
+        bool on = false;
+        if (p.res_bins) {
+            const float rb = __ldg(p.res_bins + row);
+            cqr = half_range(rb);
+            on = rb > 0.0f && cqr >= 1.0f && cqr <= cqf;
+        }
+        if (on) {
+            group_mask = static_cast<uint32_t>(p.delta_group) * 4u - 1u;  // on four times the token index
+            for (int m = tid; m < p.lp - 1; m += kThreads)
+                lut[CG_MAX_LP + m] = __fdiv_rn(__fsub_rn(static_cast<float>(m), cqf), cqr);
+        } else {
+            group_mask = 0u;
+        }
+    }
     const int cq = cqf >= 0.0f && cqf < 64.0f ? static_cast<int>(cqf) : 64;
     const int rows = table_rows(p.lp, full_levels < 2 ? 2 : full_levels);  // the register levels read entries 1..3
     uint32_t *tabs[NS];
@@ -375,12 +397,26 @@ decode_dequant_multi_kernel(const __grid_constant__ FusedDecodeParams p, int sca
     int ntok_r = ntok;
     // keep the loop's invariants in registers instead of re-deriving them from kernel parameters
     asm volatile("" : "+l"(o_token), "+r"(lut_k), "+r"(sc_a), "+r"(ntok_r));
-    auto emit = [&](const uint32_t (&a)[NS], uint32_t) {
+    float anchor[NS];
+#pragma unroll
+    for (int i = 0; i < NS; ++i) anchor[i] = 0.0f;
+    auto emit = [&](const uint32_t (&a)[NS], uint32_t t4) {
         // ((sym - Cq) / Cq) * max in fp32, then one round-to-nearest cast (cachegen_decoder.py:30-33,171-173)
         const float s = ldsf32(sc_a);
         float v[NS];
+        if (!DELTA || (t4 & group_mask) == 0u) {
 #pragma unroll
-        for (int i = 0; i < NS; ++i) v[i] = __fmul_rn(ldsf32((a[i] >> 7) + lut_k - i * (kThreads / 32)), s);
+            for (int i = 0; i < NS; ++i) {
+                v[i] = __fmul_rn(ldsf32((a[i] >> 7) + lut_k - i * (kThreads / 32)), s);
+                if (DELTA)  // what the encoder subtracted from the group's other tokens: the value in the KV dtype
+                    anchor[i] = scale_dt == CG_BF16 ? Half16<CG_BF16>::to_float(Half16<CG_BF16>::from_float(v[i]))
+                                                    : Half16<CG_F16>::to_float(Half16<CG_F16>::from_float(v[i]));
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < NS; ++i)
+                v[i] = __fadd_rn(anchor[i], __fmul_rn(ldsf32((a[i] >> 7) + lut_k - i * (kThreads / 32) + 4u * CG_MAX_LP), s));
+        }
         if (NS == 2) {
             *reinterpret_cast<uint32_t *>(o) = pack_pair<OUT_DT>(v[0], v[1]);
         } else {
@@ -473,15 +509,15 @@ static bool multi_layout_ok(const FusedDecodeParams &p, int ns) {
     return true;
 }
 
-template <int NS, int OUT_DT>
+template <int NS, int OUT_DT, bool DELTA>
 static int launch_fused_multi(const FusedDecodeParams &p, int scale_dt, cudaStream_t st) {
     const int full = search_levels(p.lp);
     const size_t smem = table_bytes(p.lp, full < 2 ? 2 : full);
     const dim3 grid(p.nslab, 2 * p.nlayers, p.njobs), block(kGroup / NS);
     if (smem > 48 * 1024)
-        cudaFuncSetAttribute(decode_dequant_multi_kernel<NS, OUT_DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(decode_dequant_multi_kernel<NS, OUT_DT, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              static_cast<int>(smem));
-    decode_dequant_multi_kernel<NS, OUT_DT><<<grid, block, smem, st>>>(p, scale_dt, full);
+    decode_dequant_multi_kernel<NS, OUT_DT, DELTA><<<grid, block, smem, st>>>(p, scale_dt, full);
     return check_launch();
 }
 
@@ -558,6 +594,8 @@ static int fused_params(const cg_decode_job *jobs_host, int njobs, int nlayers, 
     p.nchannels = nheads * head_size;
     p.lp = lp;
     p.nslab = (p.nchannels + kGroup - 1) / kGroup;
+    p.delta_group = 0;
+    p.res_bins = nullptr;
     p.bins = bins;
     p.o_layer = o_layer;
     p.o_kv = o_kv;
@@ -585,9 +623,14 @@ static int fused_params(const cg_decode_job *jobs_host, int njobs, int nlayers, 
 }
 
 static int launch_fused_any(const FusedDecodeParams &p, int scale_dtype, int out_dtype, cudaStream_t st) {
+    if (p.delta_group > 0) {  // only the two-channels-per-thread kernel knows about anchors
+        if (!multi_layout_ok(p, 2)) return CG_E_ALIGN;
+        return out_dtype == CG_F16 ? launch_fused_multi<2, CG_F16, true>(p, scale_dtype, st)
+                                   : launch_fused_multi<2, CG_BF16, true>(p, scale_dtype, st);
+    }
     if (multi_layout_ok(p, 2))
-        return out_dtype == CG_F16 ? launch_fused_multi<2, CG_F16>(p, scale_dtype, st)
-                                   : launch_fused_multi<2, CG_BF16>(p, scale_dtype, st);
+        return out_dtype == CG_F16 ? launch_fused_multi<2, CG_F16, false>(p, scale_dtype, st)
+                                   : launch_fused_multi<2, CG_BF16, false>(p, scale_dtype, st);
     if (scale_dtype == CG_F16 && out_dtype == CG_F16) return launch_fused<CG_F16, CG_F16>(p, st);
     if (scale_dtype == CG_F16 && out_dtype == CG_BF16) return launch_fused<CG_F16, CG_BF16>(p, st);
     if (scale_dtype == CG_BF16 && out_dtype == CG_F16) return launch_fused<CG_BF16, CG_F16>(p, st);
@@ -602,6 +645,24 @@ extern "C" int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int 
     if (int rc = fused_params(jobs_host, njobs, nlayers, nheads, head_size, lp, bins, scale_dtype, out_dtype,
                               o_layer, o_kv, o_token, o_head, status, p))
         return rc;
+    return launch_fused_any(p, scale_dtype, out_dtype, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int cg_decode_dequant_delta(const cg_decode_job *jobs_host, int njobs, int nlayers, int nheads,
+                                       int head_size, int lp, const float *bins, int delta_group,
+                                       const float *res_bins, int scale_dtype, int out_dtype, int64_t o_layer,
+                                       int64_t o_kv, int64_t o_token, int64_t o_head, int32_t *status, void *stream) {
+    FusedDecodeParams p;
+    if (int rc = fused_params(jobs_host, njobs, nlayers, nheads, head_size, lp, bins, scale_dtype, out_dtype,
+                              o_layer, o_kv, o_token, o_head, status, p))
+        return rc;
+    if (delta_group) {
+        if (!res_bins) return CG_E_NULL;
+        if (delta_group < 2 || delta_group > CG_MAX_TOKENS_PER_STREAM || CG_MAX_TOKENS_PER_STREAM % delta_group)
+            return CG_E_SHAPE;
+        p.delta_group = delta_group;
+        p.res_bins = res_bins;
+    }
     return launch_fused_any(p, scale_dtype, out_dtype, static_cast<cudaStream_t>(stream));
 }
 

@@ -54,6 +54,89 @@ __global__ void __launch_bounds__(256) row_absmax_kernel(const uint16_t *__restr
     if (lane == 0) scales[wid] = static_cast<uint16_t>(best);
 }
 
+// ---- anchor-token delta (no counterpart in the reference, see cg_quantize_cdf_delta in the header) -------
+// What a decoder holds for one element of an anchor token: quantise as the plain path does, then
+// ((sym - Cq) / Cq) * max in fp32 and one cast to the KV dtype.  lut[s] = (s - Cq) / Cq.
+template <int DT>
+__device__ __forceinline__ float anchor_value(uint16_t xa, float factor_a, float cqa, uint32_t keep, float max_a,
+                                              const float *lut) {
+    const float p = __fmul_rn(Half16<DT>::to_float(xa), factor_a);
+    const uint32_t s = __float_as_uint(__fadd_rn(__fadd_rn(p, cqa), 8388608.0f)) & keep;
+    return Half16<DT>::to_float(Half16<DT>::from_float(__fmul_rn(lut[s & 63u], max_a)));
+}
+// The residual of one element against its anchor, rounded to the KV dtype.
+template <int DT>
+__device__ __forceinline__ uint16_t residual_bits(uint16_t x, float anchor) {
+    return Half16<DT>::from_float(__fsub_rn(Half16<DT>::to_float(x), anchor));
+}
+// A row is delta-coded when its residual bin count gives 1 <= Cq_r <= Cq_a.
+__device__ __forceinline__ bool delta_row(const float *res_bins, int row, float cqa, float *cqr) {
+    if (!res_bins) return false;
+    const float rb = __ldg(res_bins + row);
+    if (!(rb > 0.0f)) return false;
+    *cqr = half_range(rb);
+    return *cqr >= 1.0f && *cqr <= cqa;
+}
+
+// One warp per (row, token): for the non-anchor tokens of delta rows, replaces scales[row, token]
+// (written by row_absmax_kernel, whose values for the anchors are read here) by max|residual|.
+template <int DT, int VEC>
+__global__ void __launch_bounds__(256) residual_absmax_kernel(const uint16_t *__restrict__ kv, const KvLayout L,
+                                                              const float *__restrict__ bins,
+                                                              const float *__restrict__ res_bins, int group,
+                                                              uint16_t *scales) {
+    __shared__ float luts[8][64];
+    const int64_t wid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const int nrows = 2 * L.nlayers;
+    if (wid >= static_cast<int64_t>(nrows) * L.ntokens) return;
+    const int row = static_cast<int>(wid / L.ntokens), t = static_cast<int>(wid % L.ntokens);
+    const int ta = t - t % group;
+    const float cqa = half_range(__ldg(bins + row));
+    float cqr;
+    if (t == ta || !delta_row(res_bins, row, cqa, &cqr)) return;
+    float *lut = luts[w];
+    lut[lane] = __fdiv_rn(__fsub_rn(static_cast<float>(lane), cqa), cqa);
+    lut[lane + 32] = __fdiv_rn(__fsub_rn(static_cast<float>(lane + 32), cqa), cqa);
+    __syncwarp();
+    const int layer = row % L.nlayers, j = row / L.nlayers;
+    const uint16_t *base = kv + layer * L.s_layer + j * L.s_kv;
+    const uint16_t *xt = base + t * L.s_token, *xa = base + ta * L.s_token;
+    const uint16_t ma_bits = scales[static_cast<int64_t>(row) * L.ntokens + ta];
+    const float max_a = Half16<DT>::to_float(ma_bits);
+    const float factor_a = __fdiv_rn(cqa, max_a);
+    const uint32_t keep = ma_bits ? 0xFFu : 0u;
+    uint32_t best = 0;
+    if (VEC == 8) {
+        const int per_head = L.head_size / 8;
+        const int nvec = L.nheads * per_head;
+        for (int v = lane; v < nvec; v += 32) {
+            const int h = v / per_head, d = (v - h * per_head) * 8;
+            const uint4 qt = __ldg(reinterpret_cast<const uint4 *>(xt + h * L.s_head + d));
+            const uint4 qa = __ldg(reinterpret_cast<const uint4 *>(xa + h * L.s_head + d));
+            const uint32_t wt[4] = {qt.x, qt.y, qt.z, qt.w}, wa[4] = {qa.x, qa.y, qa.z, qa.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const uint16_t a = static_cast<uint16_t>(wa[e >> 1] >> ((e & 1) * 16));
+                const uint16_t x = static_cast<uint16_t>(wt[e >> 1] >> ((e & 1) * 16));
+                const uint32_t r = residual_bits<DT>(x, anchor_value<DT>(a, factor_a, cqa, keep, max_a, lut));
+                best = max(best, r & 0x7FFFu);
+            }
+        }
+    } else {
+        const int C = L.nheads * L.head_size;
+        for (int c = lane; c < C; c += 32) {
+            const int h = c / L.head_size, d = c - h * L.head_size;
+            const uint16_t a = __ldg(xa + h * L.s_head + d), x = __ldg(xt + h * L.s_head + d);
+            const uint32_t r = residual_bits<DT>(x, anchor_value<DT>(a, factor_a, cqa, keep, max_a, lut));
+            best = max(best, r & 0x7FFFu);
+        }
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) best = max(best, __shfl_xor_sync(0xFFFFFFFFu, best, d));
+    if (lane == 0) scales[wid] = static_cast<uint16_t>(best);
+}
+
 // Counts to table (normalize_cdf_value, cal_cdf.cu:11-15,40-49), one thread per channel.
 // hist: shared uint32 [max_bins+1][kGroup], hist[v+1][c] = #{sym == v}.  Writes the channel's
 // lp = max_bins+1 entries to out16 (shared uint16 [kGroup][lp]).
@@ -90,13 +173,17 @@ constexpr int kQuantThreads = 256;
 
 // grid (nslab, nrows).  VEC = 8: every thread quantises 8 adjacent channels of one token per step
 // (one 128-bit load, one 64-bit symbol store); VEC = 1: scalar fallback for odd shapes.
-template <int DT, int VEC>
+// DELTA: rows with residual bins (res_bins[row] > 0) quantise every token that is not the first of its
+// group of `group` as a residual against its dequantised anchor, with Cq_r = res_bins // 2 - 1 and
+// the symbols moved up by Cq_a - Cq_r so that both kinds of token centre on Cq_a.
+template <int DT, int VEC, bool DELTA>
 __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
     const uint16_t *__restrict__ kv, const KvLayout L, const float *__restrict__ bins,
     const uint16_t *__restrict__ scales, int max_bins, int8_t *__restrict__ sym_out,
     int16_t *__restrict__ cdf_out, uint8_t *__restrict__ counts_out, const int64_t *__restrict__ table_row_off,
-    int32_t *status) {
+    int32_t *status, const float *__restrict__ res_bins, int group) {
     extern __shared__ uint32_t hist[];  // [max_bins+1][kGroup], then uint16 tables [kGroup][lp]
+    __shared__ float lut_a[64];
     const int lp = max_bins + 1;
     uint16_t *out16 = reinterpret_cast<uint16_t *>(hist + lp * kGroup);
     const int tid = threadIdx.x;
@@ -110,6 +197,13 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
     const uint16_t *base = kv + layer * L.s_layer + j * L.s_kv;
     const uint16_t *srow = scales + static_cast<int64_t>(row) * T;
     int8_t *orow = sym_out + static_cast<int64_t>(row) * T * C;
+    float cqr = MAX;
+    const bool delta = DELTA && delta_row(res_bins, row, MAX, &cqr);
+    const uint32_t shift = static_cast<uint32_t>(MAX - cqr);
+    if (DELTA) {
+        if (tid < 64) lut_a[tid] = __fdiv_rn(__fsub_rn(static_cast<float>(tid), MAX), MAX);
+        __syncthreads();
+    }
 
     if (VEC == 8) {
         constexpr int kLanesPerToken = kGroup / 8;                     // 16
@@ -124,18 +218,38 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
         if (c < C) {
             for (int t = tsub; t < T; t += kTokensPerStep) {
                 const uint16_t mbits = __ldg(srow + t);
-                const float factor = __fdiv_rn(MAX, Half16<DT>::to_float(mbits));
+                const bool resid = DELTA && delta && (t % group) != 0;
+                const float mq = resid ? cqr : MAX;
+                const float factor = __fdiv_rn(mq, Half16<DT>::to_float(mbits));
                 const uint32_t keep = mbits ? 0xFFu : 0u;  // all-zero token: 0 * inf = NaN -> symbol 0
                 const uint4 x = __ldg(reinterpret_cast<const uint4 *>(base + t * L.s_token + h * L.s_head + d));
-                const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+                uint32_t w[4] = {x.x, x.y, x.z, x.w};
+                if (resid) {  // the token's residuals against its dequantised anchor, in the KV dtype
+                    const int ta = t - t % group;
+                    const uint16_t ma_bits = __ldg(srow + ta);
+                    const float max_a = Half16<DT>::to_float(ma_bits);
+                    const float factor_a = __fdiv_rn(MAX, max_a);
+                    const uint32_t keep_a = ma_bits ? 0xFFu : 0u;
+                    const uint4 xa = __ldg(reinterpret_cast<const uint4 *>(base + ta * L.s_token + h * L.s_head + d));
+                    const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w};
+#pragma unroll
+                    for (int e = 0; e < 8; e += 2) {
+                        const uint32_t lo = residual_bits<DT>(static_cast<uint16_t>(w[e >> 1]),
+                                                              anchor_value<DT>(static_cast<uint16_t>(wa[e >> 1]), factor_a, MAX, keep_a, max_a, lut_a));
+                        const uint32_t hi = residual_bits<DT>(static_cast<uint16_t>(w[e >> 1] >> 16),
+                                                              anchor_value<DT>(static_cast<uint16_t>(wa[e >> 1] >> 16), factor_a, MAX, keep_a, max_a, lut_a));
+                        w[e >> 1] = lo | (hi << 16);
+                    }
+                }
+                const uint32_t up = resid ? shift : 0u;
                 uint64_t packed = 0;
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const uint16_t hb = static_cast<uint16_t>(w[e >> 1] >> ((e & 1) * 16));
                     // three separately rounded fp32 operations, then round-half-even (enc.py:56-57)
                     const float p = __fmul_rn(Half16<DT>::to_float(hb), factor);
-                    const float qv = __fadd_rn(p, MAX);
-                    const uint32_t s = __float_as_uint(__fadd_rn(qv, 8388608.0f)) & keep;
+                    const float qv = __fadd_rn(p, mq);
+                    const uint32_t s = ((__float_as_uint(__fadd_rn(qv, 8388608.0f)) & keep) + up) & 0xFFu;
                     packed |= static_cast<uint64_t>(s) << (8 * e);
                 }
                 *reinterpret_cast<uint64_t *>(orow + static_cast<int64_t>(t) * C + c) = packed;
@@ -154,11 +268,20 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
         if (c < C) {
             for (int t = tsub; t < T; t += kQuantThreads / kGroup) {
                 const uint16_t mbits = __ldg(srow + t);
-                const float factor = __fdiv_rn(MAX, Half16<DT>::to_float(mbits));
-                const uint16_t hb = __ldg(base + t * L.s_token + h * L.s_head + d);
+                const bool resid = DELTA && delta && (t % group) != 0;
+                const float mq = resid ? cqr : MAX;
+                const float factor = __fdiv_rn(mq, Half16<DT>::to_float(mbits));
+                uint16_t hb = __ldg(base + t * L.s_token + h * L.s_head + d);
+                if (resid) {
+                    const int ta = t - t % group;
+                    const uint16_t ma_bits = __ldg(srow + ta);
+                    const float max_a = Half16<DT>::to_float(ma_bits);
+                    hb = residual_bits<DT>(hb, anchor_value<DT>(__ldg(base + ta * L.s_token + h * L.s_head + d),
+                                                                __fdiv_rn(MAX, max_a), MAX, ma_bits ? 0xFFu : 0u, max_a, lut_a));
+                }
                 const float p = __fmul_rn(Half16<DT>::to_float(hb), factor);
-                const float qv = __fadd_rn(p, MAX);
-                const uint32_t s = mbits ? (__float_as_uint(__fadd_rn(qv, 8388608.0f)) & 0xFFu) : 0u;
+                const float qv = __fadd_rn(p, mq);
+                const uint32_t s = ((mbits ? (__float_as_uint(__fadd_rn(qv, 8388608.0f)) & 0xFFu) : 0u) + (resid ? shift : 0u)) & 0xFFu;
                 orow[static_cast<int64_t>(t) * C + c] = static_cast<int8_t>(s);
                 if (s < static_cast<uint32_t>(max_bins)) atomicAdd(&hist[(s + 1) * kGroup + cl], 1u);
             }
@@ -269,16 +392,36 @@ int launch_absmax(const uint16_t *x, const QuantShape &q, uint16_t *sc, cudaStre
 
 int launch_quantize(const uint16_t *x, int dtype, const QuantShape &q, const float *bins, const uint16_t *sc,
                     int max_bins, int8_t *sym_out, int16_t *cdf_out, uint8_t *counts_out,
-                    const int64_t *table_row_off, int32_t *status, cudaStream_t st) {
+                    const int64_t *table_row_off, int32_t *status, cudaStream_t st, const float *res_bins = nullptr,
+                    int group = 0) {
     const int C = q.L.nheads * q.L.head_size;
     const dim3 grid((C + kGroup - 1) / kGroup, 2 * q.L.nlayers);
     const size_t smem = hist_smem_bytes(max_bins);
-#define CG_LAUNCH_Q(DT, V) \
-    quantize_cdf_kernel<DT, V><<<grid, kQuantThreads, smem, st>>>(x, q.L, bins, sc, max_bins, sym_out, cdf_out, \
-                                                                  counts_out, table_row_off, status)
-    if (dtype == CG_F16) { if (q.vec) CG_LAUNCH_Q(CG_F16, 8); else CG_LAUNCH_Q(CG_F16, 1); }
-    else { if (q.vec) CG_LAUNCH_Q(CG_BF16, 8); else CG_LAUNCH_Q(CG_BF16, 1); }
+#define CG_LAUNCH_Q(DT, V, D) \
+    quantize_cdf_kernel<DT, V, D><<<grid, kQuantThreads, smem, st>>>(x, q.L, bins, sc, max_bins, sym_out, cdf_out, \
+                                                                     counts_out, table_row_off, status, res_bins, group)
+    if (group > 0) {
+        if (dtype == CG_F16) { if (q.vec) CG_LAUNCH_Q(CG_F16, 8, true); else CG_LAUNCH_Q(CG_F16, 1, true); }
+        else { if (q.vec) CG_LAUNCH_Q(CG_BF16, 8, true); else CG_LAUNCH_Q(CG_BF16, 1, true); }
+    } else {
+        if (dtype == CG_F16) { if (q.vec) CG_LAUNCH_Q(CG_F16, 8, false); else CG_LAUNCH_Q(CG_F16, 1, false); }
+        else { if (q.vec) CG_LAUNCH_Q(CG_BF16, 8, false); else CG_LAUNCH_Q(CG_BF16, 1, false); }
+    }
 #undef CG_LAUNCH_Q
+    return check_launch();
+}
+
+int launch_residual_absmax(const uint16_t *x, int dtype, const QuantShape &q, const float *bins,
+                           const float *res_bins, int group, uint16_t *sc, cudaStream_t st) {
+    const int64_t nwarps = static_cast<int64_t>(2 * q.L.nlayers) * q.L.ntokens;
+    const unsigned blocks = static_cast<unsigned>((nwarps * 32 + 255) / 256);
+    if (dtype == CG_F16) {
+        if (q.vec) residual_absmax_kernel<CG_F16, 8><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc);
+        else residual_absmax_kernel<CG_F16, 1><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc);
+    } else {
+        if (q.vec) residual_absmax_kernel<CG_BF16, 8><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc);
+        else residual_absmax_kernel<CG_BF16, 1><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc);
+    }
     return check_launch();
 }
 
@@ -329,4 +472,29 @@ extern "C" int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64
     uint16_t *sc = static_cast<uint16_t *>(scales_out);
     if (int rc = launch_absmax(x, q, sc, st)) return rc;
     return launch_quantize(x, dtype, q, bins, sc, max_bins, sym_out, cdf_out, counts_out, table_row_off, status, st);
+}
+
+extern "C" int cg_quantize_cdf_delta(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
+                                     int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
+                                     const float *bins, int max_bins, int delta_group, const float *res_bins,
+                                     int8_t *sym_out, void *scales_out, int16_t *cdf_out, uint8_t *counts_out,
+                                     const int64_t *table_row_off, int32_t *status, void *stream) {
+    if (delta_group == 0)
+        return cg_quantize_cdf(kv, dtype, s_layer, s_kv, s_token, s_head, nlayers, ntokens, nheads, head_size, bins,
+                               max_bins, sym_out, scales_out, cdf_out, counts_out, table_row_off, status, stream);
+    if (!kv || !bins || !res_bins || !sym_out || !scales_out || !cdf_out) return CG_E_NULL;
+    if (counts_out && !table_row_off) return CG_E_NULL;
+    if (delta_group < 2 || delta_group > CG_MAX_TOKENS_PER_STREAM || CG_MAX_TOKENS_PER_STREAM % delta_group)
+        return CG_E_SHAPE;
+    if (max_bins < 1 || max_bins >= CG_MAX_LP) return CG_E_LP;
+    QuantShape q;
+    if (int rc = quant_shape(kv, dtype, s_layer, s_kv, s_token, s_head, nlayers, ntokens, nheads, head_size, sym_out, &q))
+        return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint16_t *x = static_cast<const uint16_t *>(kv);
+    uint16_t *sc = static_cast<uint16_t *>(scales_out);
+    if (int rc = launch_absmax(x, q, sc, st)) return rc;
+    if (int rc = launch_residual_absmax(x, dtype, q, bins, res_bins, delta_group, sc, st)) return rc;
+    return launch_quantize(x, dtype, q, bins, sc, max_bins, sym_out, cdf_out, counts_out, table_row_off, status, st,
+                           res_bins, delta_group);
 }

@@ -1,6 +1,7 @@
 """Drop-in for lmcache.storage_backend.serde, cachegen codec only
 (reference: LMCache/lmcache/storage_backend/serde/__init__.py:7-28)."""
 from ..config import GlobalConfig, LMCacheEngineConfig, LMCacheEngineMetadata
+from .cachegen_basics import DeltaCoding  # noqa: F401
 from .cachegen_basics import CacheGenConfig, CacheGenGPUBytestream, CacheGenGPUEncoderOutput
 from .cachegen_decoder import CacheGenDeserializer
 from .cachegen_encoder import CacheGenSerializer
@@ -23,4 +24,4 @@ def CreateSerde(serde_type: str, config: LMCacheEngineConfig, metadata: LMCacheE
 
 
 __all__ = ["Serializer", "Deserializer", "CacheGenDeserializer", "CacheGenSerializer", "CacheGenConfig",
-           "CacheGenGPUBytestream", "CacheGenGPUEncoderOutput", "CreateSerde"]
+           "CacheGenGPUBytestream", "CacheGenGPUEncoderOutput", "CreateSerde", "DeltaCoding"]

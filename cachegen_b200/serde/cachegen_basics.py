@@ -87,6 +87,44 @@ class CacheGenConfig:
             raise ValueError(f"Model {model_name} is not supported")
 
 
+class DeltaCoding:
+    """Settings of anchor-token delta coding (cg_quantize_cdf_delta / cg_decode_dequant_delta; the
+    reference has no such step, so chunks written with it are only readable by this package and only by a
+    deserializer given the same settings).
+
+    group:    tokens per group, a power of two in 2..256; the first token of a group is the anchor
+    divisor:  residual tokens use max(4, bins // divisor) bins
+    rows:     "keys" (key rows only: keys are the smooth ones) or "all"
+    """
+
+    def __init__(self, group: int, divisor: int = 2, rows: str = "keys"):
+        if group < 2 or group > CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK or group & (group - 1):
+            raise ValueError(f"delta group must be a power of two in 2..256, got {group}")
+        if divisor < 1:
+            raise ValueError("delta divisor must be at least 1")
+        if rows not in ("keys", "all"):
+            raise ValueError(f"delta rows must be 'keys' or 'all', got {rows!r}")
+        self.group, self.divisor, self.rows = int(group), int(divisor), rows
+        self._res_bins = {}
+
+    def residual_bins(self, key_bins: torch.Tensor, value_bins: torch.Tensor, device) -> torch.Tensor:
+        """float32 [2L] on `device`: residual bin counts of the key rows then the value rows, 0 = no delta."""
+        key = (str(device), key_bins.numel(), value_bins.numel())
+        t = self._res_bins.get(key)
+        if t is None:
+            kb, vb = key_bins.detach().cpu().float(), value_bins.detach().cpu().float()
+            res_k = torch.clamp(torch.div(kb, self.divisor, rounding_mode="floor"), min=4.0)
+            res_v = torch.clamp(torch.div(vb, self.divisor, rounding_mode="floor"), min=4.0)
+            if self.rows == "keys":
+                res_v = torch.zeros_like(res_v)
+            t = torch.cat((res_k, res_v)).to(device=device, dtype=torch.float32).contiguous()
+            self._res_bins[key] = t
+        return t
+
+    def __repr__(self):
+        return f"DeltaCoding(group={self.group}, divisor={self.divisor}, rows={self.rows!r})"
+
+
 def make_key_bins(config: CacheGenConfig, device="cuda") -> torch.Tensor:
     """float32 [L] (cachegen_encoder.py:311-316 / cachegen_decoder.py:122-127)."""
     ret = torch.zeros(config.key_third_layers)

@@ -117,7 +117,7 @@ def _to_device(t: torch.Tensor, dev) -> torch.Tensor:
 class _ChunkView:
     """What a decode needs from one encoded chunk, whichever container it came in, on the GPU."""
 
-    def __init__(self, eo, dev, bins_cpu):
+    def __init__(self, eo, dev, bins_cpu, delta=None):
         self.keep = []
         if isinstance(eo, flat_format.FlatChunk):
             fc = eo if eo.blob.device == dev else eo.to(dev, non_blocking=True)
@@ -129,9 +129,13 @@ class _ChunkView:
             self.mk, self.mv = sc[:h.L], sc[h.L:]
             self.tables = fc.tables()
             self.table_kind = h.table_kind
-            if (h.table_kind != flat_format.TABLES_CDF and h.bins_checksum and
+            if ((h.table_kind != flat_format.TABLES_CDF or delta is not None) and h.bins_checksum and
+                    h.bins_checksum != flat_format.bins_checksum(bins_cpu, delta)):
+                raise RuntimeError("the container was written with other bin or delta settings")
+            if (delta is None and h.table_kind == flat_format.TABLES_CDF and h.bins_checksum and
                     h.bins_checksum != flat_format.bins_checksum(bins_cpu)):
-                raise RuntimeError("the container's byte-count tables were written with other bin settings")
+                # int16 tables decode with any bins, but a chunk written with delta coding does not
+                raise RuntimeError("the container was written with other bin or delta settings")
             if h.table_kind == flat_format.TABLES_COUNTS:
                 need = flat_format.table_row_offsets(bins_cpu, self.C)[-1]
                 if h.off_lengths - h.off_tables < need:
@@ -191,7 +195,7 @@ class DecodePlan:
 
     def __init__(self, encoder_outputs: list, bins: torch.Tensor, fmt: str,
                  out_dtype: torch.dtype, out: torch.Tensor = None, workspace: dict = None, device=None,
-                 peer_out: bool = False):
+                 peer_out: bool = False, delta=None):
         if not encoder_outputs:
             raise RuntimeError("nothing to decode")
         if fmt not in ("vllm", "huggingface"):
@@ -205,7 +209,7 @@ class DecodePlan:
             bins_cpu = bins.cpu()
             ws["bins_cpu"] = bins_cpu
         with torch.cuda.device(dev):
-            views = [_ChunkView(eo, dev, bins_cpu) for eo in encoder_outputs]
+            views = [_ChunkView(eo, dev, bins_cpu, delta) for eo in encoder_outputs]
         v0 = views[0]
         L, C, lp, H, D, scale_dtype = v0.L, v0.C, v0.lp, v0.H, v0.D, v0.scale_dtype
         NL = 2 * L
@@ -285,6 +289,11 @@ class DecodePlan:
             batch = jobs_all[b:b + _lib.CG_MAX_DECODE_JOBS]
             self.batches.append(((_lib.DecodeJob * len(batch))(*batch), len(batch),
                                  ctypes.c_void_p(goff.data_ptr() + 8 * b * ngroups)))
+        self.delta_group, self.res_bins = 0, None
+        if delta is not None:
+            self.delta_group = delta.group
+            self.res_bins = delta.residual_bins(bins[:L], bins[L:], dev)
+            self.keep.append(self.res_bins)
         self.out, self.dev, self.bins, self.status, self.goff = out, dev, bins, status, goff
         self.dims = (L, H, D, C, lp, NL, total_T)
         self.strides = (o_layer, o_kv, o_token, o_head)
@@ -312,9 +321,15 @@ class DecodePlan:
         with torch.cuda.device(self.dev):
             st = _stream(self.dev)
             for arr, n, _ in self.batches:
-                rc = lib.cg_decode_dequant(arr, n, L, H, D, lp, ctypes.c_void_p(self.bins.data_ptr()),
-                                           self.dtypes[0], self.dtypes[1], o_layer, o_kv, o_token, o_head,
-                                           ctypes.c_void_p(self.status.data_ptr()), st)
+                if self.delta_group:
+                    rc = lib.cg_decode_dequant_delta(arr, n, L, H, D, lp, ctypes.c_void_p(self.bins.data_ptr()),
+                                                     self.delta_group, ctypes.c_void_p(self.res_bins.data_ptr()),
+                                                     self.dtypes[0], self.dtypes[1], o_layer, o_kv, o_token, o_head,
+                                                     ctypes.c_void_p(self.status.data_ptr()), st)
+                else:
+                    rc = lib.cg_decode_dequant(arr, n, L, H, D, lp, ctypes.c_void_p(self.bins.data_ptr()),
+                                               self.dtypes[0], self.dtypes[1], o_layer, o_kv, o_token, o_head,
+                                               ctypes.c_void_p(self.status.data_ptr()), st)
                 _lib.check(rc, "cg_decode_dequant")
 
     def run(self) -> torch.Tensor:
@@ -331,7 +346,7 @@ class DecodePlan:
 
 
 def decode_many(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Tensor, fmt: str,
-                out_dtype: torch.dtype, out: torch.Tensor = None, workspace: dict = None) -> torch.Tensor:
+                out_dtype: torch.dtype, out: torch.Tensor = None, workspace: dict = None, delta=None) -> torch.Tensor:
     """Fused decode of consecutive encoded chunks of one KV cache into one blob.
 
     The chunks' tokens are laid one after the other along the token axis of the result, which has
@@ -345,7 +360,7 @@ def decode_many(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Ten
     `out`, when given, must have the result's shape and dtype with a unit innermost stride (any other
     strides).  `workspace` caches the small offset / status buffers between calls.
     """
-    return DecodePlan(encoder_outputs, bins, fmt, out_dtype, out=out, workspace=workspace).run()
+    return DecodePlan(encoder_outputs, bins, fmt, out_dtype, out=out, workspace=workspace, delta=delta).run()
 
 
 _copy_streams = {}
@@ -357,7 +372,7 @@ def _chunk_tokens(eo) -> int:
 
 def decode_many_pipelined(encoder_outputs: List[CacheGenGPUEncoderOutput], bins: torch.Tensor, fmt: str,
                           out_dtype: torch.dtype, out: torch.Tensor = None, groups: int = 4,
-                          workspaces: list = None) -> torch.Tensor:
+                          workspaces: list = None, delta=None) -> torch.Tensor:
     """decode_many for encoded chunks held in pinned host memory, with the host-to-device copies of
     one group of chunks overlapped with the decode of the previous group (a copy stream per device;
     the decode launches stay on the caller's current stream).  `workspaces`: one dict per group."""
@@ -393,7 +408,7 @@ def decode_many_pipelined(encoder_outputs: List[CacheGenGPUEncoderOutput], bins:
         view = out[:, :, t0:t0 + tg] if fmt == "vllm" else out[:, :, :, t0:t0 + tg]
         with torch.cuda.stream(copy_stream):
             part = _stage_flat(part, workspaces[g], dev)
-            plan = DecodePlan(part, bins, fmt, out_dtype, out=view, workspace=workspaces[g], device=dev)
+            plan = DecodePlan(part, bins, fmt, out_dtype, out=view, workspace=workspaces[g], device=dev, delta=delta)
             ready = torch.cuda.Event()
             ready.record(copy_stream)
         cur.wait_event(ready)
@@ -425,9 +440,9 @@ def _stage_flat(part: list, ws: dict, dev) -> list:
 
 
 def decode_to_kv(encoder_output: CacheGenGPUEncoderOutput, bins: torch.Tensor, fmt: str, out_dtype: torch.dtype,
-                 out: torch.Tensor = None, workspace: dict = None) -> torch.Tensor:
+                 out: torch.Tensor = None, workspace: dict = None, delta=None) -> torch.Tensor:
     """Fused decode of one encoded chunk into its KV blob (see decode_many)."""
-    return decode_many([encoder_output], bins, fmt, out_dtype, out=out, workspace=workspace)
+    return decode_many([encoder_output], bins, fmt, out_dtype, out=out, workspace=workspace, delta=delta)
 
 
 class CacheGenDeserializer(Deserializer):
@@ -435,8 +450,10 @@ class CacheGenDeserializer(Deserializer):
     fp16 for "huggingface"); `cachegen_config` replaces the lookup by model name."""
 
     def __init__(self, config: LMCacheEngineConfig, metadata: LMCacheEngineMetadata,
-                 cachegen_config: CacheGenConfig = None, out_dtype: torch.dtype = None):
+                 cachegen_config: CacheGenConfig = None, out_dtype: torch.dtype = None,
+                 delta: "CGBasics.DeltaCoding" = None):
         _lib.lib()  # fail at construction if the CUDA library is missing
+        self.delta = delta  # anchor-token delta coding: must be what the serializer was given
         self.cachegen_config = cachegen_config or CacheGenConfig.from_model_name(metadata.model_name)
         self.chunk_size = config.chunk_size
         self.fmt = metadata.fmt
@@ -461,7 +478,7 @@ class CacheGenDeserializer(Deserializer):
             # the reference slices a chunk_size-row buffer and fails in its reshape (dec.py:138-141,101)
             raise RuntimeError(f"blob holds {ntokens} tokens, more than chunk_size = {self.chunk_size}")
         return decode_to_kv(encoder_output, self._bins_on(_device_of(encoder_output)), self.fmt, self.out_dtype,
-                            out=out, workspace=self._workspace)
+                            out=out, workspace=self._workspace, delta=self.delta)
 
     def decode_many(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None) -> torch.Tensor:
         """Consecutive chunks of one KV cache into one blob, in as few launches as possible."""
@@ -469,7 +486,7 @@ class CacheGenDeserializer(Deserializer):
             if _chunk_tokens(eo) > self.chunk_size:
                 raise RuntimeError(f"a blob holds more tokens than chunk_size = {self.chunk_size}")
         return decode_many(encoder_outputs, self._bins_on(_device_of(encoder_outputs[0])), self.fmt, self.out_dtype,
-                           out=out, workspace=self._workspace)
+                           out=out, workspace=self._workspace, delta=self.delta)
 
     def decode_many_host(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None,
                          groups: int = None) -> torch.Tensor:
@@ -482,7 +499,7 @@ class CacheGenDeserializer(Deserializer):
         if len(ws) < groups:
             ws += [dict() for _ in range(groups - len(ws))]
         return decode_many_pipelined(encoder_outputs, self._bins_on(_device_of(encoder_outputs[0])), self.fmt,
-                                     self.out_dtype, out=out, groups=groups, workspaces=ws)
+                                     self.out_dtype, out=out, groups=groups, workspaces=ws, delta=self.delta)
 
     def group_status_words(self):
         """Status words of the pipelined path's per-group workspaces."""
@@ -495,7 +512,8 @@ class CacheGenDeserializer(Deserializer):
         (default: this object's) share its offset buffer: `run` recomputes the offsets every time, but
         `run_decode` alone is only valid while no other plan of the workspace has run in between."""
         return DecodePlan(encoder_outputs, self._bins_on(_device_of(encoder_outputs[0])), self.fmt, self.out_dtype,
-                          out=out, workspace=self._workspace if workspace is None else workspace, peer_out=peer_out)
+                          out=out, workspace=self._workspace if workspace is None else workspace, peer_out=peer_out,
+                          delta=self.delta)
 
     def _bins_on(self, dev) -> torch.Tensor:
         if not dev.type == "cuda":

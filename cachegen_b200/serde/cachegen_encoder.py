@@ -138,7 +138,8 @@ def row_scales(kv: torch.Tensor) -> torch.Tensor:
 
 
 def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor, max_bins: int,
-                        with_counts: bool = False, scales: torch.Tensor = None, bins_cpu: torch.Tensor = None):
+                        with_counts: bool = False, scales: torch.Tensor = None, bins_cpu: torch.Tensor = None,
+                        delta: "CGBasics.DeltaCoding" = None):
     """Fused torch_quant_vectorized (K and V) + calculate_cdf (K and V) + the two torch.cat of
     encode_function (enc.py:42-59, 257-267).
 
@@ -184,7 +185,12 @@ def quantize_and_tables(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: to
     head = (_ptr(kv), _DTYPES[kv.dtype], kv.stride(0), kv.stride(1), kv.stride(2), kv.stride(3), L, T, H, D,
             _ptr(bins), int(max_bins))
     with torch.cuda.device(dev):
-        if given:
+        if delta is not None:
+            if given:
+                raise RuntimeError("precomputed scales cannot be combined with delta coding")
+            res_bins = delta.residual_bins(key_bins, value_bins, dev)
+            rc = _lib.lib().cg_quantize_cdf_delta(*head, delta.group, _ptr(res_bins), _ptr(sym), _ptr(scales), *tail)
+        elif given:
             rc = _lib.lib().cg_quantize_cdf_scaled(*head, _ptr(scales), _ptr(sym), *tail)
         else:
             rc = _lib.lib().cg_quantize_cdf(*head, _ptr(sym), _ptr(scales), *tail)
@@ -254,10 +260,11 @@ class _PendingChunk:
     """One chunk whose quantise / table / coder kernels are enqueued but whose payload size is not
     yet known on the host."""
 
-    def __init__(self, kv, key_bins, value_bins, max_bins, scales=None):
+    def __init__(self, kv, key_bins, value_bins, max_bins, scales=None, delta=None):
         self.L, _, self.T, self.H, self.D = kv.shape
         self.dtype = kv.dtype
-        self.sym, self.scales, self.cdf = quantize_and_tables(kv, key_bins, value_bins, max_bins, scales=scales)
+        self.sym, self.scales, self.cdf = quantize_and_tables(kv, key_bins, value_bins, max_bins, scales=scales,
+                                                              delta=delta)
         NL, T, C = self.sym.shape
         dev = self.sym.device
         self.nsub = (T + CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK - 1) // CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK
@@ -310,7 +317,7 @@ class _PendingChunk:
 
 
 def encode_many(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor, chunk_tokens: int,
-                batch: int = 16, max_bins: int = None) -> list:
+                batch: int = 16, max_bins: int = None, delta=None) -> list:
     """Encodes a whole KV cache [L, 2, T, H, D] (GPU, unit innermost stride) chunk by chunk, as
     LMCacheEngine.store does with one to_bytes call per chunk (LMCache/lmcache/cache_engine.py:205-255
     in the reference), but with one host synchronisation per `batch` chunks instead of one per chunk:
@@ -322,7 +329,8 @@ def encode_many(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tens
     starts = list(range(0, T, chunk_tokens))
     result = []
     for b in range(0, len(starts), batch):
-        pending = [_PendingChunk(kv[:, :, s:s + chunk_tokens], key_bins, value_bins, kmax) for s in starts[b:b + batch]]
+        pending = [_PendingChunk(kv[:, :, s:s + chunk_tokens], key_bins, value_bins, kmax, delta=delta)
+                   for s in starts[b:b + batch]]
         host = torch.cat([p.tail for p in pending]).cpu()  # the batch's one synchronisation
         pos = 0
         for p in pending:
@@ -352,14 +360,14 @@ def encode_levels(kv: torch.Tensor, levels: list) -> list:
 
 @_lmcache_nvtx_annotate
 def encode_function(kv: torch.Tensor, config: CacheGenConfig, key_bins: torch.Tensor, value_bins: torch.Tensor,
-                    chunk_size: int, max_bins: int = None) -> CacheGenGPUEncoderOutput:
+                    chunk_size: int, max_bins: int = None, delta=None) -> CacheGenGPUEncoderOutput:
     """Encodes one chunk of KV, [L, 2, T, H, D] on the GPU, T == chunk_size (enc.py:247-301)."""
     num_heads, head_size = kv.shape[-2:]
     L = kv.shape[0]
     if kv.shape[2] != chunk_size:
         raise RuntimeError(f"chunk_size {chunk_size} does not match the {kv.shape[2]} tokens of the blob")
     kmax = _table_bins(key_bins, value_bins, max_bins)
-    sym, scales, cdf = quantize_and_tables(kv, key_bins, value_bins, kmax)
+    sym, scales, cdf = quantize_and_tables(kv, key_bins, value_bins, kmax, delta=delta)
     stream_bytes, lengths, offs = encode_streams(cdf, sym)
     data_chunks = []
     step = CGBasics.CACHEGEN_GPU_MAX_TOKENS_PER_CHUNK
@@ -401,7 +409,7 @@ def pack_sparse_tables(counts: torch.Tensor, bins: torch.Tensor, nchannels: int,
 
 
 def encode_flat(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor,
-                compact_tables=True, max_bins: int = None) -> flat_format.FlatChunk:
+                compact_tables=True, max_bins: int = None, delta=None) -> flat_format.FlatChunk:
     """Encodes one chunk of KV, [L, 2, T, H, D] on the GPU, into a CGB2 container on the GPU
     (flat_format.py): the same tables, lengths and streams as encode_function, with uint16 lengths and
     the tables in the smallest form that can hold them.  compact_tables: True (sparse byte counts when
@@ -413,7 +421,7 @@ def encode_flat(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tens
     bins = torch.cat((key_bins, value_bins)).to(device=kv.device, dtype=torch.float32).contiguous()
     bins_cpu = bins.cpu()
     sym, scales, cdf, counts, qstatus = quantize_and_tables(kv, key_bins, value_bins, kmax, with_counts=True,
-                                                            bins_cpu=bins_cpu)
+                                                            bins_cpu=bins_cpu, delta=delta)
     try_sparse = compact_tables is True and flat_format.sparse_representable(bins_cpu)
     if try_sparse:
         sparse, written, off_counts = pack_sparse_tables(counts, bins, C, bins_cpu)
@@ -429,7 +437,7 @@ def encode_flat(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tens
     else:
         kind, tables = flat_format.TABLES_CDF, cdf.view(torch.uint8).reshape(-1)
     header = flat_format.layout(L, H, D, T, kmax + 1, kv.dtype, kind, tables.numel(), flat_format.LENGTHS_U16, offs,
-                                bins_checksum=flat_format.bins_checksum(bins_cpu))
+                                bins_checksum=flat_format.bins_checksum(bins_cpu, delta))
     # zeroed, so that the alignment gaps between the sections are defined: the same KV gives the same bytes
     blob = torch.zeros(header.total, dtype=torch.uint8, device=kv.device)
     head = header.pack()
@@ -451,10 +459,12 @@ class CacheGenSerializer(Serializer):
     cannot read)."""
 
     def __init__(self, config: LMCacheEngineConfig, metadata: LMCacheEngineMetadata,
-                 cachegen_config: CacheGenConfig = None, wire_format: str = "pickle", table_max_bins: int = None):
+                 cachegen_config: CacheGenConfig = None, wire_format: str = "pickle", table_max_bins: int = None,
+                 delta: "CGBasics.DeltaCoding" = None):
         if wire_format not in ("pickle", "flat"):
             raise ValueError(f"unknown wire format {wire_format!r}")
         self.wire_format = wire_format
+        self.delta = delta  # anchor-token delta coding: off (None) is the reference's behaviour
         self.table_max_bins = table_max_bins  # see _table_bins: set for a layer shard of a model
         _lib.lib()  # fail at construction if the CUDA library is missing
         self.cachegen_config = cachegen_config or CacheGenConfig.from_model_name(metadata.model_name)
@@ -475,7 +485,7 @@ class CacheGenSerializer(Serializer):
             tensor = tensor.permute(0, 1, 3, 2, 4)  # a view; the kernels read it through its strides
         ntokens = tensor.shape[2]
         return encode_function(tensor.cuda(), self.cachegen_config, self.key_bins, self.value_bins, ntokens,
-                               max_bins=self.table_max_bins)
+                               max_bins=self.table_max_bins, delta=self.delta)
 
     def encode_many(self, tensor: torch.Tensor, chunk_tokens: int = None, batch: int = 16) -> list:
         """A whole KV cache, one encoded chunk per `chunk_tokens` (default: the configured chunk size)
@@ -486,7 +496,7 @@ class CacheGenSerializer(Serializer):
         if tensor.stride(4) != 1:
             tensor = tensor.contiguous()
         return encode_many(tensor, self.key_bins, self.value_bins, chunk_tokens or self.chunk_size, batch,
-                           max_bins=self.table_max_bins)
+                           max_bins=self.table_max_bins, delta=self.delta)
 
     def encode_levels(self, tensor: torch.Tensor, cachegen_configs: list) -> list:
         """The chunk encoded with each of `cachegen_configs` (CacheGenConfig objects, e.g. the three
@@ -505,7 +515,8 @@ class CacheGenSerializer(Serializer):
         tensor = tensor.cuda()
         if tensor.stride(4) != 1:
             tensor = tensor.contiguous()
-        return encode_flat(tensor, self.key_bins, self.value_bins, compact_tables, max_bins=self.table_max_bins)
+        return encode_flat(tensor, self.key_bins, self.value_bins, compact_tables, max_bins=self.table_max_bins,
+                           delta=self.delta)
 
     @_lmcache_nvtx_annotate
     def to_bytes(self, tensor: torch.Tensor) -> bytes:

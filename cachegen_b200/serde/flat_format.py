@@ -62,11 +62,15 @@ def table_row_offsets(bins_cpu: torch.Tensor, nchannels: int) -> List[int]:
     return offs
 
 
-def bins_checksum(bins_cpu: torch.Tensor) -> int:
-    """Non-zero 32-bit checksum of the per-row bin counts (key rows then value rows).  The byte-count
-    table forms can only be read with the bins they were written with; the header carries this so
-    that a decoder configured otherwise refuses the container instead of misreading it."""
-    return zlib.crc32(struct.pack(f"<{bins_cpu.numel()}H", *[int(b) for b in bins_cpu.tolist()])) or 1
+def bins_checksum(bins_cpu: torch.Tensor, delta=None) -> int:
+    """Non-zero 32-bit checksum of the per-row bin counts (key rows then value rows) and of the
+    anchor-token delta settings, if any.  The byte-count table forms and delta-coded chunks can only be
+    read with the settings they were written with; the header carries this so that a decoder
+    configured otherwise refuses the container instead of misreading it."""
+    raw = struct.pack(f"<{bins_cpu.numel()}H", *[int(b) for b in bins_cpu.tolist()])
+    if delta is not None:
+        raw += struct.pack("<HHB", delta.group, delta.divisor, 1 if delta.rows == "all" else 0)
+    return zlib.crc32(raw) or 1
 
 
 def mask_row_offsets(bins_cpu: torch.Tensor, nchannels: int) -> List[int]:

@@ -217,6 +217,26 @@ int cg_quantize_cdf_scaled(const void *kv, int dtype, int64_t s_layer, int64_t s
                            int32_t *status, void *stream);
 
 /*
+ * cg_quantize_cdf with anchor-token delta coding.  No counterpart in the reference, whose serializer
+ * quantises every token on its own (cachegen_encoder.py:42-59); delta_group == 0 is exactly
+ * cg_quantize_cdf.  With delta_group = G (a power of two, 2..256): in every row r with
+ * res_bins[r] > 0 (float32 [2*L] on the device, 1 <= res_bins[r] // 2 - 1 <= bins[r] // 2 - 1), token t
+ * of the call with t % G != 0 is coded as its difference from the DEQUANTISED first token a of its
+ * group, as a decoder reconstructs it:
+ *     x^a = cast(((sym_a - Cq_a) / Cq_a) * max_a)       r = cast(float(x_t) - float(x^a))
+ *     max_t = amax|r|    sym_t = round(float(r) * (Cq_r / max_t) + Cq_r) + (Cq_a - Cq_r)
+ * (casts to the KV dtype; Cq_a = bins[r] // 2 - 1, Cq_r = res_bins[r] // 2 - 1).  scales_out holds
+ * max_t of the residual for those tokens; symbols of both kinds centre on Cq_a and share the row's
+ * tables.  Other rows and the first token of every group are quantised as cg_quantize_cdf does.
+ * The decoder must be given the same delta_group and res_bins (cg_decode_dequant_delta).  Three launches.
+ */
+int cg_quantize_cdf_delta(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
+                          int64_t s_head, int nlayers, int ntokens, int nheads, int head_size,
+                          const float *bins, int max_bins, int delta_group, const float *res_bins,
+                          int8_t *sym_out, void *scales_out, int16_t *cdf_out, uint8_t *counts_out,
+                          const int64_t *table_row_off, int32_t *status, void *stream);
+
+/*
  * Byte counts (CG_TABLES_COUNTS, as cg_quantize_cdf writes them) -> CG_TABLES_SPARSE parts.  No
  * counterpart in the reference.  counts / count_row_off [nrows]: the dense counts and their row
  * offsets; bins: float32 [nrows] on the device.  group_off_out: uint32 [nrows * ceil(nchannels/128) + 1];
@@ -311,6 +331,21 @@ int cg_decode_dequant(const cg_decode_job *jobs_host, int njobs, int nlayers, in
                       int head_size, int lp, const float *bins, int scale_dtype, int out_dtype,
                       int64_t o_layer, int64_t o_kv, int64_t o_token, int64_t o_head,
                       int32_t *status, void *stream);
+
+/*
+ * cg_decode_dequant for chunks written by cg_quantize_cdf_delta (no counterpart in the reference;
+ * delta_group == 0 is exactly cg_decode_dequant).  In rows with res_bins[r] > 0 a token that is not the
+ * first of its group of delta_group decodes to
+ *     cast_out(float(cast_kv(v_anchor)) + ((sym - Cq_a) / Cq_r) * max_t)
+ * where v_anchor is the fp32 value of the group's first token and cast_kv rounds to scale_dtype, the
+ * KV dtype the encoder saw.  Every job must start on a group boundary (sub-chunks of 256 tokens do).
+ * Needs the layout of the two-channels-per-thread kernel: even head_size and strides, 4-byte aligned
+ * output (CG_E_ALIGN otherwise).
+ */
+int cg_decode_dequant_delta(const cg_decode_job *jobs_host, int njobs, int nlayers, int nheads,
+                            int head_size, int lp, const float *bins, int delta_group,
+                            const float *res_bins, int scale_dtype, int out_dtype, int64_t o_layer,
+                            int64_t o_kv, int64_t o_token, int64_t o_head, int32_t *status, void *stream);
 
 /*
  * No counterpart in the reference.  The same work as cg_decode_offsets followed by cg_decode_dequant,

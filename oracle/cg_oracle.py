@@ -37,6 +37,10 @@ def lib():
         _lib.cgo_quantize.restype = None
         _lib.cgo_dequantize.argtypes = [p, i64, i64, i64, i32, i32, i32, p, p, i32, p, i64, i64, i64, i32]
         _lib.cgo_dequantize.restype = None
+        _lib.cgo_quantize_delta.argtypes = [p, i32, i32, i32, i32, p, p, i32, p, p]
+        _lib.cgo_quantize_delta.restype = i32
+        _lib.cgo_dequantize_delta.argtypes = [p, i32, i32, i32, p, p, i32, p, i32, p, i64, i64, i64, i32]
+        _lib.cgo_dequantize_delta.restype = None
         _lib.cgo_calculate_cdf.argtypes = [p, i64, i64, i64, i32, i32, i32, i32, p]
         _lib.cgo_calculate_cdf.restype = i32
         _lib.cgo_encode_stream.argtypes = [p, i32, p, i64, i32, p, i64, p]
@@ -93,6 +97,37 @@ def quantize(x_bits, bins, dtype=F16):
     maxes = np.empty((rows, T, 1), dtype=np.uint16)
     lib().cgo_quantize(_ptr(x_bits), dtype, rows, T, C, _ptr(bins), _ptr(sym), _ptr(maxes))
     return sym, maxes
+
+
+def quantize_delta(x_bits, bins, res_bins, group, dtype=F16):
+    """Anchor-token delta quantiser (cgo_quantize_delta): rows with res_bins > 0 code every token that is
+    not the first of its group of `group` as a residual against the dequantised anchor."""
+    x_bits = np.ascontiguousarray(x_bits, dtype=np.uint16)
+    rows, T, C = x_bits.shape
+    bins = np.ascontiguousarray(bins, dtype=np.float32)
+    res_bins = np.ascontiguousarray(res_bins, dtype=np.float32)
+    assert bins.shape == (rows,) and res_bins.shape == (rows,)
+    sym = np.empty((rows, T, C), dtype=np.int8)
+    maxes = np.empty((rows, T, 1), dtype=np.uint16)
+    rc = lib().cgo_quantize_delta(_ptr(x_bits), dtype, rows, T, C, _ptr(bins), _ptr(res_bins), int(group), _ptr(sym),
+                                  _ptr(maxes))
+    if rc:
+        raise ValueError("bad delta settings (group < 1, or residual bins outside [4, bins])")
+    return sym, maxes
+
+
+def dequantize_delta(sym, bins, res_bins, group, maxes, max_dtype=F16, out_dtype=F16):
+    """The decoder's side of quantize_delta: uint16 bits [rows, T, C]."""
+    rows, T, C = sym.shape
+    sym = np.ascontiguousarray(sym.view(np.uint8))
+    bins = np.ascontiguousarray(bins, dtype=np.float32)
+    res_bins = np.ascontiguousarray(res_bins, dtype=np.float32)
+    maxes = np.ascontiguousarray(maxes, dtype=np.uint16).reshape(rows, T)
+    out = np.empty((rows, T, C), dtype=np.uint16)
+    st = _estrides(out)
+    lib().cgo_dequantize_delta(_ptr(sym), rows, T, C, _ptr(bins), _ptr(res_bins), int(group), _ptr(maxes), max_dtype,
+                               _ptr(out), st[0], st[1], st[2], out_dtype)
+    return out
 
 
 def dequantize(sym, bins, maxes, max_dtype=F16, out_dtype=F16, out=None, out_strides=None):
