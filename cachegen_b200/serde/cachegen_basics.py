@@ -235,20 +235,36 @@ def _owns_its_storage(t: torch.Tensor) -> bool:
             t.dtype in torch.storage._dtype_to_storage_type_map())
 
 
+_PLACEHOLDER_LEN = 1 << 16  # pickle writes byte strings of at least this size outside its frames
+
+
 class _BlobPickler(pickle.Pickler):
     """Pickles the tensors whose bytes are in `raw_of` (by id) from those bytes; everything else as
-    pickle.dump does."""
+    pickle.dump does.  A large storage stream is not built here: a placeholder byte string of
+    _PLACEHOLDER_LEN bytes stands in for it (pickle frames it the same way: outside the frames) and
+    `deferred` remembers, by the placeholder's id, the stream's head and raw bytes; _assemble puts
+    them in place, so the tensor's bytes are copied once, into the final blob."""
 
     def __init__(self, file, raw_of: dict):
         super().__init__(file)
         self.raw_of = raw_of
+        self.deferred = {}
+        self.keep = []
 
     def reducer_override(self, obj):
         if isinstance(obj, torch.Tensor) and id(obj) in self.raw_of:
             from collections import OrderedDict
             head = _legacy_stream_head(obj.dtype, str(obj.untyped_storage()._cdata),
                                        torch.serialization.location_tag(obj.untyped_storage()), obj.numel())
-            storage = _StreamedStorage(b"".join((head, self.raw_of[id(obj)])))
+            raw = self.raw_of[id(obj)]
+            n = len(head) + len(raw)
+            if _PLACEHOLDER_LEN <= n < (1 << 32):
+                stream = bytes(_PLACEHOLDER_LEN)
+                self.deferred[id(stream)] = (head, raw, n)
+                self.keep.append(stream)  # ids must stay unique until the blob is assembled
+            else:
+                stream = b"".join((head, raw))
+            storage = _StreamedStorage(stream)
             return (torch._utils._rebuild_tensor_v2,
                     (storage, 0, tuple(obj.size()), obj.stride(), False, OrderedDict()))
         return NotImplemented
@@ -264,6 +280,51 @@ class _PartsWriter:
     def write(self, b):
         self.parts.append(b if isinstance(b, bytes) else bytes(b))
         return len(b)
+
+
+def _assemble(parts: list, deferred: dict) -> bytes:
+    """The blob from the pickler's writes, every placeholder replaced by its stream: the 4-byte length
+    before it is corrected, then everything is copied once into a new bytes object -- the large pieces
+    by torch's multi-threaded copy, which also spreads the page faults of the fresh allocation."""
+    import ctypes
+    import struct
+    pieces = []  # (bytes-like, length)
+    for i, part in enumerate(parts):
+        d = deferred.get(id(part))
+        if d is None:
+            pieces.append(part)
+            continue
+        head, raw, n = d
+        prev = pieces[-1]
+        marker = b"B" + struct.pack("<I", _PLACEHOLDER_LEN)  # BINBYTES + length, the last thing written before the payload
+        if not prev.endswith(marker):
+            raise RuntimeError("unexpected pickle layout around a storage stream")
+        pieces[-1] = prev[:-4] + struct.pack("<I", n)
+        pieces.append(head)
+        pieces.append(raw)
+    total = sum(len(x) for x in pieces)
+    api = ctypes.pythonapi
+    api.PyBytes_FromStringAndSize.restype = ctypes.py_object
+    api.PyBytes_FromStringAndSize.argtypes = [ctypes.c_char_p, ctypes.c_ssize_t]
+    api.PyBytes_AsString.restype = ctypes.c_void_p
+    api.PyBytes_AsString.argtypes = [ctypes.py_object]
+    blob = api.PyBytes_FromStringAndSize(None, total)  # uninitialised, ours alone until it is returned
+    base = api.PyBytes_AsString(blob)
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        dst = torch.frombuffer((ctypes.c_ubyte * total).from_address(base), dtype=torch.uint8) if total else None
+    pos = 0
+    for x in pieces:
+        n = len(x)
+        if n >= (1 << 20):
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")  # a read-only source buffer, and it is only read
+                dst[pos:pos + n].copy_(torch.frombuffer(x, dtype=torch.uint8))
+        elif n:
+            ctypes.memmove(base + pos, bytes(x) if not isinstance(x, bytes) else x, n)
+        pos += n
+    return blob
 
 
 def dump_blob(eo: "CacheGenGPUEncoderOutput") -> bytes:
@@ -294,8 +355,9 @@ def dump_blob(eo: "CacheGenGPUEncoderOutput") -> bytes:
         if id(t) not in raw_of:
             raw_of[id(t)] = memoryview(t.reshape(-1).view(torch.uint8).numpy()) if t.numel() else b""
     out = _PartsWriter()
-    _BlobPickler(out, raw_of).dump(eo)
-    blob = b"".join(out.parts)
+    pickler = _BlobPickler(out, raw_of)
+    pickler.dump(eo)
+    blob = _assemble(out.parts, pickler.deferred)
     if on_gpu:
         st.end()
     return blob
