@@ -551,9 +551,10 @@ struct EncoderState {
         span32 = 0u;
         pending = 0u;
     }
-    // one symbol s in [0, maxsym] (enc_new.cu:257-295); the table column must have a readable row
-    // after the last symbol's.  lanes: the warp's lanes that encode together (same token count).
-    CG_HD void step(Smem sm, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out, uint32_t lanes) {
+    // One symbol s in [0, maxsym] (enc_new.cu:257-295), any state, any number of output bits; stores
+    // whole words as needed but leaves up to 63 bits in the accumulator.  The table column must have
+    // a readable row after the last symbol's.
+    CG_HD void step_general(Smem sm, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out) {
         const uint32_t a = col + s * kTableRowBytes;
         const uint32_t flo = scale_exact(span32, sm.ld(a));
         const uint32_t fnext = scale_exact(span32, sm.ld(a + kTableRowBytes));
@@ -568,17 +569,11 @@ struct EncoderState {
             const uint32_t bits = low >> (32u - n1);
             const uint32_t first = bits >> (n1 - 1u);
             const uint32_t rest = bits & ((1u << (n1 - 1u)) - 1u);
-            const uint32_t total = n1 + pending;
-            if (total <= kFastEmitBits) {
-                const uint32_t run = ((1u << pending) - 1u) & (first - 1u);  // pending ones after a 0, zeros after a 1
-                out.put((first << (total - 1u)) | (run << (n1 - 1u)) | rest, total);
-            } else {
-                out.drain();
-                out.put(first, 1u);
-                out.put_run(1u - first, pending);
-                out.drain();
-                out.put(rest, n1 - 1u);
-            }
+            out.drain();
+            out.put(first, 1u);
+            out.put_run(1u - first, pending);
+            out.drain();
+            out.put(rest, n1 - 1u);
             pending = 0u;
         }
         // underflow shifts (enc_new.cu:288-293) only raise the pending count; both kinds of shift
@@ -588,8 +583,48 @@ struct EncoderState {
         const uint32_t sh = (n1 + k) & 31u;
         low = (low << sh) & 0x7FFFFFFFu;
         span32 <<= sh;
-        // a store for every lane that has a full word, as soon as one lane is near the high-water mark
-        if (cg_any_lane(lanes, out.nacc >= kSinkHighWater)) {
+    }
+    // The same symbol in straight-line code for the usual case -- the range is not the full 2^32 (it is
+    // only for a stream's first symbol, and after a shift that lands on it exactly) and at most
+    // kFastEmitBits bits come out -- with one warp vote for everything else: a lane outside the usual
+    // case takes the step again from its saved state through step_general, and every lane with a
+    // full word stores it as soon as one lane is near the accumulator's high-water mark, so that the
+    // store is not a per-lane branch either.  lanes: the warp's lanes that encode together.
+    CG_HD void step(Smem sm, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out, uint32_t lanes) {
+        const EncoderState before = *this;
+        const uint64_t acc_before = out.acc;
+        const uint32_t nacc_before = out.nacc;
+        const uint32_t a = col + s * kTableRowBytes;
+        const uint32_t flo = cg_umulhi(span32, sm.ld(a));
+        const uint32_t fnext = cg_umulhi(span32, sm.ld(a + kTableRowBytes));
+        const uint32_t fhi = (s == maxsym) ? span32 : fnext;
+        low += flo;
+        span32 = fhi - flo;
+        const uint32_t high = low + span32 - 1u;
+        const uint32_t n1 = static_cast<uint32_t>(equal_shifts(low, high));
+        const uint32_t k = static_cast<uint32_t>(cg_clz((cg_shl((~low) | high, n1) << 1) | 1u));
+        // output: low's top bit, then the pending bits as its inverse, then low's next n1 - 1 bits; nothing
+        // when n1 == 0
+        const bool has = n1 != 0u;
+        const uint32_t total = n1 + pending;
+        const bool redo = before.span32 == 0u || (has && total > kFastEmitBits);
+        const uint32_t first = low >> 31;
+        const uint32_t n1m = n1 - (has ? 1u : 0u);
+        const uint32_t rest = cg_fshl(low, 0u, n1) & ((1u << n1m) - 1u);
+        const uint32_t head = (1u << (pending & 31u)) - 1u + first;  // first, then `pending` copies of its inverse
+        const bool emit = has && !redo;
+        out.put(emit ? ((head << n1m) | rest) : 0u, emit ? total : 0u);
+        pending = (has ? 0u : pending) + k;
+        const uint32_t sh = (n1 + k) & 31u;
+        low = (low << sh) & 0x7FFFFFFFu;
+        span32 <<= sh;
+        if (cg_any_lane(lanes, redo || out.nacc >= kSinkHighWater)) {
+            if (redo) {
+                *this = before;
+                out.acc = acc_before;
+                out.nacc = nacc_before;
+                step_general(sm, col, s, maxsym, out);
+            }
             if (out.nacc >= 32u) out.store_word();
         }
     }

@@ -22,13 +22,15 @@ __device__ __forceinline__ uint32_t absmax2(uint32_t best, uint32_t packed) {
 }
 
 // One warp per (row, token).  scales[row, token] gets the 16-bit pattern of max|x|.
+// Rows row0 .. row0 + nrows - 1 (the host walks the rows in windows small enough for L2, so that the
+// quantise pass that follows a window finds its KV there).
 template <int VEC>
 __global__ void __launch_bounds__(256) row_absmax_kernel(const uint16_t *__restrict__ kv, const KvLayout L,
-                                                         uint16_t *__restrict__ scales) {
-    const int64_t wid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+                                                         uint16_t *__restrict__ scales, int row0, int nrows) {
+    int64_t wid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    const int nrows = 2 * L.nlayers;
     if (wid >= static_cast<int64_t>(nrows) * L.ntokens) return;
+    wid += static_cast<int64_t>(row0) * L.ntokens;
     const int row = static_cast<int>(wid / L.ntokens), t = static_cast<int>(wid % L.ntokens);
     const int layer = row % L.nlayers, j = row / L.nlayers;
     const uint16_t *base = kv + layer * L.s_layer + j * L.s_kv + t * L.s_token;
@@ -84,12 +86,12 @@ template <int DT, int VEC>
 __global__ void __launch_bounds__(256) residual_absmax_kernel(const uint16_t *__restrict__ kv, const KvLayout L,
                                                               const float *__restrict__ bins,
                                                               const float *__restrict__ res_bins, int group,
-                                                              uint16_t *scales) {
+                                                              uint16_t *scales, int row0, int nrows) {
     __shared__ float luts[8][64];
-    const int64_t wid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    int64_t wid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    const int nrows = 2 * L.nlayers;
     if (wid >= static_cast<int64_t>(nrows) * L.ntokens) return;
+    wid += static_cast<int64_t>(row0) * L.ntokens;
     const int row = static_cast<int>(wid / L.ntokens), t = static_cast<int>(wid % L.ntokens);
     const int ta = t - t % group;
     const float cqa = half_range(__ldg(bins + row));
@@ -181,13 +183,13 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
     const uint16_t *__restrict__ kv, const KvLayout L, const float *__restrict__ bins,
     const uint16_t *__restrict__ scales, int max_bins, int8_t *__restrict__ sym_out,
     int16_t *__restrict__ cdf_out, uint8_t *__restrict__ counts_out, const int64_t *__restrict__ table_row_off,
-    int32_t *status, const float *__restrict__ res_bins, int group) {
+    int32_t *status, const float *__restrict__ res_bins, int group, int row0) {
     extern __shared__ uint32_t hist[];  // [max_bins+1][kGroup], then uint16 tables [kGroup][lp]
     __shared__ float lut_a[64];
     const int lp = max_bins + 1;
     uint16_t *out16 = reinterpret_cast<uint16_t *>(hist + lp * kGroup);
     const int tid = threadIdx.x;
-    const int row = blockIdx.y, c0 = blockIdx.x * kGroup;
+    const int row = row0 + blockIdx.y, c0 = blockIdx.x * kGroup;
     const int C = L.nheads * L.head_size, T = L.ntokens;
     const int layer = row % L.nlayers, j = row / L.nlayers;
     for (int i = tid; i < lp * kGroup; i += kQuantThreads) hist[i] = 0u;
@@ -382,24 +384,35 @@ int quant_shape(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_
     return CG_OK;
 }
 
-int launch_absmax(const uint16_t *x, const QuantShape &q, uint16_t *sc, cudaStream_t st) {
-    const int64_t nwarps = static_cast<int64_t>(2 * q.L.nlayers) * q.L.ntokens;
+// Rows of one window of the quantise passes: as many as keep the window's KV within about a third of
+// the 126 MB L2 (the passes over a window read it two or three times and write its symbols).
+int window_rows(const QuantShape &q) {
+    const int64_t row_bytes = static_cast<int64_t>(q.L.ntokens) * q.L.nheads * q.L.head_size * 2;
+    const int64_t fit = (40ll << 20) / (row_bytes > 0 ? row_bytes : 1);
+    const int nrows = 2 * q.L.nlayers;
+    return static_cast<int>(fit < 1 ? 1 : (fit > nrows ? nrows : fit));
+}
+
+int launch_absmax(const uint16_t *x, const QuantShape &q, uint16_t *sc, cudaStream_t st, int row0 = 0, int nrows = -1) {
+    if (nrows < 0) nrows = 2 * q.L.nlayers;
+    const int64_t nwarps = static_cast<int64_t>(nrows) * q.L.ntokens;
     const unsigned ablocks = static_cast<unsigned>((nwarps * 32 + 255) / 256);
-    if (q.vec) row_absmax_kernel<8><<<ablocks, 256, 0, st>>>(x, q.L, sc);
-    else row_absmax_kernel<1><<<ablocks, 256, 0, st>>>(x, q.L, sc);
+    if (q.vec) row_absmax_kernel<8><<<ablocks, 256, 0, st>>>(x, q.L, sc, row0, nrows);
+    else row_absmax_kernel<1><<<ablocks, 256, 0, st>>>(x, q.L, sc, row0, nrows);
     return check_launch();
 }
 
 int launch_quantize(const uint16_t *x, int dtype, const QuantShape &q, const float *bins, const uint16_t *sc,
                     int max_bins, int8_t *sym_out, int16_t *cdf_out, uint8_t *counts_out,
                     const int64_t *table_row_off, int32_t *status, cudaStream_t st, const float *res_bins = nullptr,
-                    int group = 0) {
+                    int group = 0, int row0 = 0, int nrows = -1) {
+    if (nrows < 0) nrows = 2 * q.L.nlayers;
     const int C = q.L.nheads * q.L.head_size;
-    const dim3 grid((C + kGroup - 1) / kGroup, 2 * q.L.nlayers);
+    const dim3 grid((C + kGroup - 1) / kGroup, nrows);
     const size_t smem = hist_smem_bytes(max_bins);
 #define CG_LAUNCH_Q(DT, V, D) \
     quantize_cdf_kernel<DT, V, D><<<grid, kQuantThreads, smem, st>>>(x, q.L, bins, sc, max_bins, sym_out, cdf_out, \
-                                                                     counts_out, table_row_off, status, res_bins, group)
+                                                                     counts_out, table_row_off, status, res_bins, group, row0)
     if (group > 0) {
         if (dtype == CG_F16) { if (q.vec) CG_LAUNCH_Q(CG_F16, 8, true); else CG_LAUNCH_Q(CG_F16, 1, true); }
         else { if (q.vec) CG_LAUNCH_Q(CG_BF16, 8, true); else CG_LAUNCH_Q(CG_BF16, 1, true); }
@@ -412,15 +425,15 @@ int launch_quantize(const uint16_t *x, int dtype, const QuantShape &q, const flo
 }
 
 int launch_residual_absmax(const uint16_t *x, int dtype, const QuantShape &q, const float *bins,
-                           const float *res_bins, int group, uint16_t *sc, cudaStream_t st) {
-    const int64_t nwarps = static_cast<int64_t>(2 * q.L.nlayers) * q.L.ntokens;
+                           const float *res_bins, int group, uint16_t *sc, cudaStream_t st, int row0, int nrows) {
+    const int64_t nwarps = static_cast<int64_t>(nrows) * q.L.ntokens;
     const unsigned blocks = static_cast<unsigned>((nwarps * 32 + 255) / 256);
     if (dtype == CG_F16) {
-        if (q.vec) residual_absmax_kernel<CG_F16, 8><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc);
-        else residual_absmax_kernel<CG_F16, 1><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc);
+        if (q.vec) residual_absmax_kernel<CG_F16, 8><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc, row0, nrows);
+        else residual_absmax_kernel<CG_F16, 1><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc, row0, nrows);
     } else {
-        if (q.vec) residual_absmax_kernel<CG_BF16, 8><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc);
-        else residual_absmax_kernel<CG_BF16, 1><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc);
+        if (q.vec) residual_absmax_kernel<CG_BF16, 8><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc, row0, nrows);
+        else residual_absmax_kernel<CG_BF16, 1><<<blocks, 256, 0, st>>>(x, q.L, bins, res_bins, group, sc, row0, nrows);
     }
     return check_launch();
 }
@@ -470,8 +483,15 @@ extern "C" int cg_quantize_cdf(const void *kv, int dtype, int64_t s_layer, int64
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint16_t *x = static_cast<const uint16_t *>(kv);
     uint16_t *sc = static_cast<uint16_t *>(scales_out);
-    if (int rc = launch_absmax(x, q, sc, st)) return rc;
-    return launch_quantize(x, dtype, q, bins, sc, max_bins, sym_out, cdf_out, counts_out, table_row_off, status, st);
+    const int total = 2 * nlayers, step = window_rows(q);
+    for (int r0 = 0; r0 < total; r0 += step) {
+        const int n = total - r0 < step ? total - r0 : step;
+        if (int rc = launch_absmax(x, q, sc, st, r0, n)) return rc;
+        if (int rc = launch_quantize(x, dtype, q, bins, sc, max_bins, sym_out, cdf_out, counts_out, table_row_off,
+                                     status, st, nullptr, 0, r0, n))
+            return rc;
+    }
+    return CG_OK;
 }
 
 extern "C" int cg_quantize_cdf_delta(const void *kv, int dtype, int64_t s_layer, int64_t s_kv, int64_t s_token,
@@ -493,8 +513,14 @@ extern "C" int cg_quantize_cdf_delta(const void *kv, int dtype, int64_t s_layer,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint16_t *x = static_cast<const uint16_t *>(kv);
     uint16_t *sc = static_cast<uint16_t *>(scales_out);
-    if (int rc = launch_absmax(x, q, sc, st)) return rc;
-    if (int rc = launch_residual_absmax(x, dtype, q, bins, res_bins, delta_group, sc, st)) return rc;
-    return launch_quantize(x, dtype, q, bins, sc, max_bins, sym_out, cdf_out, counts_out, table_row_off, status, st,
-                           res_bins, delta_group);
+    const int total = 2 * nlayers, step = window_rows(q);
+    for (int r0 = 0; r0 < total; r0 += step) {
+        const int n = total - r0 < step ? total - r0 : step;
+        if (int rc = launch_absmax(x, q, sc, st, r0, n)) return rc;
+        if (int rc = launch_residual_absmax(x, dtype, q, bins, res_bins, delta_group, sc, st, r0, n)) return rc;
+        if (int rc = launch_quantize(x, dtype, q, bins, sc, max_bins, sym_out, cdf_out, counts_out, table_row_off,
+                                     status, st, res_bins, delta_group, r0, n))
+            return rc;
+    }
+    return CG_OK;
 }
