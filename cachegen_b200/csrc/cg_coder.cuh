@@ -586,14 +586,21 @@ struct EncoderState {
     }
     // The same symbol in straight-line code for the usual case -- the range is not the full 2^32 (it is
     // only for a stream's first symbol, and after a shift that lands on it exactly) and at most
-    // kFastEmitBits bits come out -- with one warp vote for everything else: a lane outside the usual
-    // case takes the step again from its saved state through step_general, and every lane with a
-    // full word stores it as soon as one lane is near the accumulator's high-water mark, so that the
-    // store is not a per-lane branch either.  lanes: the warp's lanes that encode together.
-    CG_HD void step(Smem sm, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out, uint32_t lanes) {
-        const EncoderState before = *this;
-        const uint64_t acc_before = out.acc;
-        const uint32_t nacc_before = out.nacc;
+    // kFastEmitBits bits come out.  step_try does the step on that assumption and says whether it held
+    // (`before` keeps what is needed to take the step again); step_finish repairs a lane for which
+    // it did not, through step_general, and stores a full word of the accumulator.  Between the two
+    // goes ONE warp vote (see step), so that neither the repair nor the store is a per-lane branch in
+    // the usual case.
+    struct Before {
+        uint32_t low, span32, pending, nacc;
+        uint64_t acc;
+    };
+    CG_HD bool step_try(Smem sm, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out, Before &before) {
+        before.low = low;
+        before.span32 = span32;
+        before.pending = pending;
+        before.nacc = out.nacc;
+        before.acc = out.acc;
         const uint32_t a = col + s * kTableRowBytes;
         const uint32_t flo = cg_umulhi(span32, sm.ld(a));
         const uint32_t fnext = cg_umulhi(span32, sm.ld(a + kTableRowBytes));
@@ -602,31 +609,44 @@ struct EncoderState {
         span32 = fhi - flo;
         const uint32_t high = low + span32 - 1u;
         const uint32_t n1 = static_cast<uint32_t>(equal_shifts(low, high));
-        const uint32_t k = static_cast<uint32_t>(cg_clz((cg_shl((~low) | high, n1) << 1) | 1u));
-        // output: low's top bit, then the pending bits as its inverse, then low's next n1 - 1 bits; nothing
-        // when n1 == 0
-        const bool has = n1 != 0u;
+        const uint32_t y = cg_shl((~low) | high, n1);
+        const uint32_t k = static_cast<uint32_t>(cg_clz(y + y));  // 32 only on a table that is not increasing
+        // Output when n1 != 0: low's top bit, then the pending bits as its inverse, then low's next
+        // n1 - 1 bits.  Everything below is computed whatever n1 is (shift counts wrap or clamp) and
+        // masked off when there is nothing to put or the step has to be taken again.
         const uint32_t total = n1 + pending;
-        const bool redo = before.span32 == 0u || (has && total > kFastEmitBits);
+        const bool has = n1 != 0u;
+        const bool redo = (before.span32 == 0u) | (has & (total > kFastEmitBits));
+        const uint32_t keep = (has & !redo) ? 0xFFFFFFFFu : 0u;
         const uint32_t first = low >> 31;
-        const uint32_t n1m = n1 - (has ? 1u : 0u);
-        const uint32_t rest = cg_fshl(low, 0u, n1) & ((1u << n1m) - 1u);
-        const uint32_t head = (1u << (pending & 31u)) - 1u + first;  // first, then `pending` copies of its inverse
-        const bool emit = has && !redo;
-        out.put(emit ? ((head << n1m) | rest) : 0u, emit ? total : 0u);
+        const uint32_t rest = cg_fshl(low + low, 0u, n1 - 1u);                 // the n1 - 1 bits after the first
+        const uint32_t head = ~cg_shl(0xFFFFFFFFu, pending) + first;            // first, then `pending` copies of its inverse
+        out.put((cg_shl(head, (n1 - 1u) & 31u) | rest) & keep, total & keep);
         pending = (has ? 0u : pending) + k;
         const uint32_t sh = (n1 + k) & 31u;
         low = (low << sh) & 0x7FFFFFFFu;
         span32 <<= sh;
-        if (cg_any_lane(lanes, redo || out.nacc >= kSinkHighWater)) {
-            if (redo) {
-                *this = before;
-                out.acc = acc_before;
-                out.nacc = nacc_before;
-                step_general(sm, col, s, maxsym, out);
-            }
-            if (out.nacc >= 32u) out.store_word();
+        return redo;
+    }
+    CG_HD void step_finish(bool redo, const Before &before, Smem sm, uint32_t col, uint32_t s, uint32_t maxsym,
+                           BitSink &out) {
+        if (redo) {
+            low = before.low;
+            span32 = before.span32;
+            pending = before.pending;
+            out.acc = before.acc;
+            out.nacc = before.nacc;
+            step_general(sm, col, s, maxsym, out);
         }
+        if (out.nacc >= 32u) out.store_word();
+    }
+    // One symbol of one stream per lane.  lanes: the warp's lanes that encode together (same token
+    // count).  Every lane with a full word stores it as soon as one lane is near the accumulator's
+    // high-water mark.
+    CG_HD void step(Smem sm, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out, uint32_t lanes) {
+        Before before;
+        const bool redo = step_try(sm, col, s, maxsym, out, before);
+        if (cg_any_lane(lanes, redo || out.nacc >= kSinkHighWater)) step_finish(redo, before, sm, col, s, maxsym, out);
     }
     // final flush (enc_new.cu:298-306); returns the stream length in bytes
     CG_HD uint32_t flush(BitSink &out) {

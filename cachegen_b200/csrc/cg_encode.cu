@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
     const int8_t *sp = p.sym + row * p.s0 + static_cast<int64_t>(t0) * p.s1 + c * p.s2;
     EncoderState enc;
     enc.init();
-    bool bad_symbol = false;
+    uint32_t largest = 0;  // the largest symbol met: one above maxsym is reported and coded as maxsym
 
     const int64_t s1 = p.s1;
     for (int base = 0; base < n; base += kPrefetch) {
@@ -55,9 +55,8 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
 #pragma unroll
         for (int j = 0; j < kPrefetch; ++j) {
             if (base + j >= n) break;
-            uint32_t s = buf[j];
-            if (s > static_cast<uint32_t>(maxsym)) { s = maxsym; bad_symbol = true; }
-            enc.step(Smem{}, col, s, static_cast<uint32_t>(maxsym), out, lanes);
+            largest = max(largest, buf[j]);
+            enc.step(Smem{}, col, min(buf[j], static_cast<uint32_t>(maxsym)), static_cast<uint32_t>(maxsym), out, lanes);
         }
     }
     const uint32_t nbytes = enc.flush(out);
@@ -65,7 +64,7 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
     if (p.status) {
         int bits = 0;
         if (static_cast<int64_t>(nbytes) > p.stride) bits |= CG_S_STREAM_OVERFLOW;
-        if (bad_symbol) bits |= CG_S_BAD_SYMBOL;
+        if (largest > static_cast<uint32_t>(maxsym)) bits |= CG_S_BAD_SYMBOL;
         if (bits) atomicOr(p.status, bits);
     }
 }
@@ -195,8 +194,9 @@ __global__ void __launch_bounds__(kGroup) compact_kernel(const uint8_t *scratch,
 using namespace cg;
 
 static int launch_encode(const EncodeParams &p, int nrows, int nsub, cudaStream_t st) {
-    const dim3 grid((p.nchannels + kGroup - 1) / kGroup, nrows, nsub), block(kGroup);
-    encode_kernel<<<grid, block, static_cast<size_t>(p.lp) * kRowBytes, st>>>(p);
+    const dim3 grid((p.nchannels + kGroup - 1) / kGroup, nrows, nsub);
+    const size_t smem = static_cast<size_t>(p.lp) * kRowBytes;
+    encode_kernel<<<grid, kGroup, smem, st>>>(p);
     return check_launch();
 }
 
