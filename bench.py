@@ -50,7 +50,7 @@ HBM_FALLBACK_GBS = 6650.0
 # 2,048-token launch and grow in proportion to the tokens of a launch; the issue figures come from a
 # 512-token launch (`--set full`, and sass__inst_executed_per_opcode).
 NCU_CAPTURE = {
-    (32, 32, 128): {"traffic_bytes_per_token": 1259.6e6 / 2048, "issue_active_pct": 64.9, "alu_pipe_pct": 59.9,
+    (32, 32, 128): {"traffic_bytes_per_token": 1255.9e6 / 2048, "issue_active_pct": 64.8, "alu_pipe_pct": 59.8,
                     "warp_instr_per_32_symbols": 56.2,
                     "source": "ncu on bench.py --tokens 2048 (dram__bytes_read.sum + dram__bytes_write.sum) and "
                               "--tokens 512 (--set full; sass__inst_executed_per_opcode), B200, kernel "

@@ -162,7 +162,10 @@ __global__ void segment_offsets_kernel(const int64_t *totals, int nsub, int64_t 
 }
 
 // ---- gather (second half of collect_bytes, cachegen_encoder.py:210-222) ------------------------------------
-// One block per (group, row, sub-chunk); every warp copies a quarter of the group's streams.
+// One block per (group, row, sub-chunk).  Eight lanes copy one stream: its scratch row is read as
+// aligned 32-bit words (one per lane and step) and written byte by byte to where the stream goes
+// (streams lie back to back, so the destination has no alignment); a warp has four streams in flight
+// and a block sixteen, which is what hides the latency of these short dependent copies.
 __global__ void __launch_bounds__(kGroup) compact_kernel(const uint8_t *scratch, int64_t stride,
                                                          const int32_t *lengths, const int64_t *group_off,
                                                          const int64_t *sub_off, int nchannels,
@@ -170,7 +173,7 @@ __global__ void __launch_bounds__(kGroup) compact_kernel(const uint8_t *scratch,
     __shared__ int warp_sums[kGroup / 32];
     __shared__ int offs[kGroup];
     __shared__ int lens[kGroup];
-    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int tid = threadIdx.x;
     const int row = blockIdx.y, sub = blockIdx.z, nrows = gridDim.y, nslab = gridDim.x;
     const int c = blockIdx.x * kGroup + tid;
     const int64_t slot0 = (static_cast<int64_t>(sub) * nrows + row) * nchannels + blockIdx.x * kGroup;
@@ -181,11 +184,19 @@ __global__ void __launch_bounds__(kGroup) compact_kernel(const uint8_t *scratch,
     __syncthreads();
     const int64_t gid = (static_cast<int64_t>(sub) * nrows + row) * nslab + blockIdx.x;
     uint8_t *dst0 = bytes_out + sub_off[sub] + group_off[gid];
-    for (int s = w; s < kGroup; s += kGroup / 32) {
-        const int n = lens[s];
-        const uint8_t *src = scratch + (slot0 + s) * stride;
+    constexpr int kLanesPerStream = 8;
+    const int part = tid % kLanesPerStream;
+    for (int s = tid / kLanesPerStream; s < kGroup; s += kGroup / kLanesPerStream) {
+        const int n = min(lens[s], static_cast<int>(stride));  // a longer stream was truncated and reported by the encoder
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(scratch + (slot0 + s) * stride);
         uint8_t *dst = dst0 + offs[s];
-        for (int j = lane; j < n; j += 32) dst[j] = src[j];
+        for (int j = part * 4; j < n; j += kLanesPerStream * 4) {
+            const uint32_t w = __ldg(src + (j >> 2));
+            dst[j] = static_cast<uint8_t>(w);
+            if (j + 1 < n) dst[j + 1] = static_cast<uint8_t>(w >> 8);
+            if (j + 2 < n) dst[j + 2] = static_cast<uint8_t>(w >> 16);
+            if (j + 3 < n) dst[j + 3] = static_cast<uint8_t>(w >> 24);
+        }
     }
 }
 
@@ -246,6 +257,8 @@ extern "C" int cg_compact_streams(const uint8_t *scratch, int64_t scratch_stride
                                   int nchannels, uint8_t *bytes_out, void *stream) {
     if (!scratch || !lengths || !group_off || !sub_off || !bytes_out) return CG_E_NULL;
     if (nsub <= 0 || nrows <= 0 || nchannels <= 0 || nrows > 65535 || nsub > 65535) return CG_E_SHAPE;
+    // the rows are read as 32-bit words, as cg_encode_chunk wrote them
+    if (scratch_stride < 4 || (scratch_stride & 3) || (reinterpret_cast<uintptr_t>(scratch) & 3)) return CG_E_ALIGN;
     const dim3 grid((nchannels + kGroup - 1) / kGroup, nrows, nsub);
     compact_kernel<<<grid, kGroup, 0, static_cast<cudaStream_t>(stream)>>>(scratch, scratch_stride, lengths,
                                                                           group_off, sub_off, nchannels, bytes_out);

@@ -227,7 +227,7 @@ class DecodePlan:
         elif (tuple(out.shape) != shape or out.dtype != out_dtype or out.stride(4) != 1 or
               (out.device != dev and not peer_out)):
             # peer_out: `out` is memory of another GPU of the box that this GPU can address
-            # (cachegen_b200.parallel.share_from_root); the kernel stores into it over NVLink
+            # (cachegen_b200.parallel.buffer_on_root); the kernel stores into it over NVLink
             raise RuntimeError("output tensor has the wrong shape, dtype, device or innermost stride")
         if fmt == "vllm":
             o_layer, o_kv, o_token, o_head = out.stride(0), out.stride(1), out.stride(2), out.stride(3)
