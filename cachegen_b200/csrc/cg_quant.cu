@@ -140,17 +140,18 @@ __global__ void __launch_bounds__(256) residual_absmax_kernel(const uint16_t *__
 }
 
 // Counts to table (normalize_cdf_value, cal_cdf.cu:11-15,40-49), one thread per channel.
-// hist: shared uint32 [max_bins+1][kGroup], hist[v+1][c] = #{sym == v}.  Writes the channel's
+// hist: shared uint32 [max_bins+1][kGroup], hist[v][c] = #{sym == v} for v < max_bins; the last row collects
+// the symbols outside the table (counted with min(sym, max_bins): no branch), which no entry reads.  Writes the channel's
 // lp = max_bins+1 entries to out16 (shared uint16 [kGroup][lp]).
 __device__ __forceinline__ void counts_to_table(const uint32_t *hist, int max_bins, int cl, uint16_t *out16) {
     const int lp = max_bins + 1;
     uint32_t total = 0;
-    for (int i = 1; i <= max_bins; ++i) total += hist[i * kGroup + cl];
+    for (int i = 0; i < max_bins; ++i) total += hist[i * kGroup + cl];
     total &= 0xFFFFu;  // the reference accumulates in uint16
     const uint32_t scale = 0xFFFFu - static_cast<uint32_t>(max_bins);
     uint32_t cum = 0;
     for (int i = 0; i <= max_bins; ++i) {
-        if (i) cum = (cum + hist[i * kGroup + cl]) & 0xFFFFu;
+        if (i) cum = (cum + hist[(i - 1) * kGroup + cl]) & 0xFFFFu;
         const uint32_t nv = total ? (scale * cum / total) : 0u;
         out16[cl * lp + i] = static_cast<uint16_t>(nv + i);
     }
@@ -259,7 +260,7 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
                 for (int e = 0; e < 8; ++e) {
                     const int ee = (e + rot) & 7;
                     const uint32_t s = static_cast<uint32_t>(packed >> (8 * ee)) & 0xFFu;
-                    if (s < static_cast<uint32_t>(max_bins)) atomicAdd(&hist[(s + 1) * kGroup + q * 8 + ee], 1u);
+                    atomicAdd(&hist[min(s, static_cast<uint32_t>(max_bins)) * kGroup + q * 8 + ee], 1u);
                 }
             }
         }
@@ -285,7 +286,7 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
                 const float qv = __fadd_rn(p, mq);
                 const uint32_t s = ((mbits ? (__float_as_uint(__fadd_rn(qv, 8388608.0f)) & 0xFFu) : 0u) + (resid ? shift : 0u)) & 0xFFu;
                 orow[static_cast<int64_t>(t) * C + c] = static_cast<int8_t>(s);
-                if (s < static_cast<uint32_t>(max_bins)) atomicAdd(&hist[(s + 1) * kGroup + cl], 1u);
+                atomicAdd(&hist[min(s, static_cast<uint32_t>(max_bins)) * kGroup + cl], 1u);
             }
         }
     }
@@ -299,7 +300,7 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
         for (int i = tid; i < 2 * cq * kGroup; i += kQuantThreads) {
             const int jj = i / kGroup, cl = i - jj * kGroup;
             const int sym = jj < cq ? jj : jj + 1;
-            const uint32_t n = (sym < max_bins) ? hist[(sym + 1) * kGroup + cl] : 0u;
+            const uint32_t n = (sym < max_bins) ? hist[sym * kGroup + cl] : 0u;
             if (c0 + cl < C) {
                 dst[static_cast<int64_t>(jj) * C + cl] = static_cast<uint8_t>(n);
                 overflow |= n > 255u;
@@ -308,7 +309,7 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
         // a symbol above 2*Cq (which the quantiser never produces) has no place in the byte counts
         for (int i = tid; i < (max_bins - 2 * cq - 1) * kGroup; i += kQuantThreads) {
             const int sym = 2 * cq + 1 + i / kGroup, cl = i % kGroup;
-            overflow |= (c0 + cl < C) && hist[(sym + 1) * kGroup + cl] != 0u;
+            overflow |= (c0 + cl < C) && hist[sym * kGroup + cl] != 0u;
         }
         if (overflow && status) atomicOr(status, CG_S_COUNT_OVERFLOW);
     }
@@ -333,7 +334,7 @@ __global__ void __launch_bounds__(kQuantThreads) symbol_cdf_kernel(const int8_t 
         const int8_t *p = sym + row * s0 + c * s2;
         for (int t = tsub; t < ntokens; t += kQuantThreads / kGroup) {
             const uint32_t s = static_cast<uint8_t>(__ldg(p + t * s1));
-            if (s < static_cast<uint32_t>(max_bins)) atomicAdd(&hist[(s + 1) * kGroup + cl], 1u);
+            atomicAdd(&hist[min(s, static_cast<uint32_t>(max_bins)) * kGroup + cl], 1u);
         }
     }
     __syncthreads();
