@@ -8,12 +8,13 @@ torch ops and per-sub-chunk launches replaced by three C-ABI calls:
     cg_encode_chunk      every sub-chunk's streams + offsets            (enc.py:269-292, 225-236)
     cg_compact_streams   gather of the streams                          (enc.py:210-222)
 
-Beside it: encode_many (a whole cache, one host synchronisation per batch of chunks), encode_levels
+Beside it: encode_many (a whole cache, up to a batch of chunks in flight and no wait in between), encode_levels
 (one chunk at several bin settings: cg_row_absmax + cg_quantize_cdf_scaled per level) and encode_flat
 (the CGB2 container of flat_format.py, tables packed by cg_pack_sparse_tables).
 
 (enc.py = cachegen_encoder.py of the reference.)
 """
+import collections
 import ctypes
 from typing import Tuple
 
@@ -317,26 +318,75 @@ class _PendingChunk:
 
 
 def encode_many(kv: torch.Tensor, key_bins: torch.Tensor, value_bins: torch.Tensor, chunk_tokens: int,
-                batch: int = 16, max_bins: int = None, delta=None) -> list:
+                batch: int = 16, max_bins: int = None, delta=None, streams: int = 3) -> list:
     """Encodes a whole KV cache [L, 2, T, H, D] (GPU, unit innermost stride) chunk by chunk, as
     LMCacheEngine.store does with one to_bytes call per chunk (LMCache/lmcache/cache_engine.py:205-255
-    in the reference), but with one host synchronisation per `batch` chunks instead of one per chunk:
-    all kernels of a batch are enqueued first, their payload sizes come back in one transfer, then the
-    streams are gathered.  Every chunk keeps its own scratch (136 MB for a 7B-shape chunk) until then.
+    in the reference), but without waiting for a chunk's payload size before the next chunk's kernels
+    are enqueued: up to `batch` chunks are in flight; a chunk's sizes come back by an asynchronous copy
+    into pinned memory, and its streams are gathered once `batch` later chunks have been enqueued, so
+    the host never waits for the GPU except at the end.  Every chunk in flight keeps its own scratch
+    (136 MB for a 7B-shape chunk).  Consecutive chunks run on `streams` side streams in turn (see
+    _side_streams); the caller's stream waits for them before the call returns.
     Returns the chunks' CacheGenGPUEncoderOutput objects, identical to per-chunk encode_function calls."""
     kmax = _table_bins(key_bins, value_bins, max_bins)
     T = kv.shape[2]
-    starts = list(range(0, T, chunk_tokens))
-    result = []
-    for b in range(0, len(starts), batch):
-        pending = [_PendingChunk(kv[:, :, s:s + chunk_tokens], key_bins, value_bins, kmax, delta=delta)
-                   for s in starts[b:b + batch]]
-        host = torch.cat([p.tail for p in pending]).cpu()  # the batch's one synchronisation
-        pos = 0
-        for p in pending:
-            result.append(p.finish(host[pos:pos + p.nsub + 2]))
-            pos += p.nsub + 2
+    caller = torch.cuda.current_stream(kv.device)
+    lanes = _side_streams(kv.device, streams)
+    for side in lanes:
+        side.wait_stream(caller)  # the cache is ready on the caller's stream
+    result, in_flight = [], collections.deque()
+
+    def finish_oldest():
+        p, host, arrived, side = in_flight.popleft()
+        arrived.synchronize()
+        with torch.cuda.stream(side):
+            out = p.finish(host)
+        # made on a side stream, used and freed by the caller on its own
+        for t in _tensors_of(out):
+            t.record_stream(caller)
+        result.append(out)
+
+    for i, s in enumerate(range(0, T, chunk_tokens)):
+        side = lanes[i % len(lanes)]
+        with torch.cuda.stream(side):
+            p = _PendingChunk(kv[:, :, s:s + chunk_tokens], key_bins, value_bins, kmax, delta=delta)
+            host = torch.empty(p.tail.shape, dtype=p.tail.dtype, pin_memory=True)
+            host.copy_(p.tail, non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(side)
+        in_flight.append((p, host, arrived, side))
+        # the oldest chunk's sizes arrived long ago: its gather queues up behind the kernels of the chunks
+        # after it, and the host work of finishing it runs while the GPU is busy with them
+        if len(in_flight) > batch:
+            finish_oldest()
+    while in_flight:
+        finish_oldest()
+    for side in lanes:
+        caller.wait_stream(side)
     return result
+
+
+_SIDE_STREAMS = {}
+
+
+def _side_streams(device, n):
+    """n streams of `device`, made once and kept: consecutive chunks of encode_many go to different
+    streams, so that one chunk's kernels fill the SMs that the last, partly filled wave of the previous
+    chunk's coder kernel leaves idle (2,048 blocks over 1,480 resident ones: 1.4 waves)."""
+    key = (torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device())
+    have = _SIDE_STREAMS.setdefault(key, [])
+    while len(have) < n:
+        have.append(torch.cuda.Stream(device=device))
+    return have[:n]
+
+
+def _tensors_of(out: CacheGenGPUEncoderOutput):
+    yield out.cdf
+    yield out.max_tensors_key
+    yield out.max_tensors_value
+    for piece in out.data_chunks:
+        yield piece.bytestream
+        yield piece.bytestream_lengths
 
 
 def encode_levels(kv: torch.Tensor, levels: list) -> list:
@@ -487,16 +537,16 @@ class CacheGenSerializer(Serializer):
         return encode_function(tensor.cuda(), self.cachegen_config, self.key_bins, self.value_bins, ntokens,
                                max_bins=self.table_max_bins, delta=self.delta)
 
-    def encode_many(self, tensor: torch.Tensor, chunk_tokens: int = None, batch: int = 16) -> list:
+    def encode_many(self, tensor: torch.Tensor, chunk_tokens: int = None, batch: int = 16, streams: int = 3) -> list:
         """A whole KV cache, one encoded chunk per `chunk_tokens` (default: the configured chunk size)
-        tokens, with one host synchronisation per `batch` chunks."""
+        tokens, with up to `batch` chunks in flight on the GPU, on `streams` streams in turn."""
         if self.fmt == "huggingface":
             tensor = tensor.permute(0, 1, 3, 2, 4)
         tensor = tensor.cuda()
         if tensor.stride(4) != 1:
             tensor = tensor.contiguous()
         return encode_many(tensor, self.key_bins, self.value_bins, chunk_tokens or self.chunk_size, batch,
-                           max_bins=self.table_max_bins, delta=self.delta)
+                           max_bins=self.table_max_bins, delta=self.delta, streams=streams)
 
     def encode_levels(self, tensor: torch.Tensor, cachegen_configs: list) -> list:
         """The chunk encoded with each of `cachegen_configs` (CacheGenConfig objects, e.g. the three
