@@ -307,12 +307,12 @@ class Harness:
         return ms if local else max_over_ranks(ms, device=self.dev)
 
 
-def make_serde(spec, world, rank, cachegen_config=None, table_max_bins=None):
+def make_serde(spec, world, rank, cachegen_config=None, table_max_bins=None, chunk_size=None):
     import torch
 
     from cachegen_b200.config import LMCacheEngineConfig, LMCacheEngineMetadata
     from cachegen_b200.serde import CacheGenDeserializer, CacheGenSerializer
-    config = LMCacheEngineConfig.from_defaults(chunk_size=CHUNK_TOKENS)
+    config = LMCacheEngineConfig.from_defaults(chunk_size=chunk_size or CHUNK_TOKENS)
     meta = LMCacheEngineMetadata(model_name=spec["model_name"], world_size=world, worker_id=rank, fmt="vllm")
     kw = {} if cachegen_config is None else {"cachegen_config": cachegen_config}
     ser = CacheGenSerializer(config, meta, table_max_bins=table_max_bins, **kw)
@@ -469,6 +469,36 @@ def leg_config3(h, args):
             "ms_per_step": ms, "tokens_per_s": T / ms * 1e3, "launches_per_step": plan.launches,
             "bytes_per_token": (plan.payload_bytes + plan.table_bytes + plan.length_bytes + plan.scale_bytes) / T,
             "roofline_frac": algorithmic / ms_kernel / 1e6 / peak, "peak_kind": kind}
+
+
+def leg_whole_context(h, spec, args):
+    """The workload through ONE serializer call over all its tokens, as the reference's evaluation scripts
+    do (run_cachegen.py:53 there: chunk_size = the context length): one table per (row, channel) built over
+    the whole context, one stream per 256-token sub-chunk.  Encode and decode of that one object."""
+    torch = h.torch
+    from cachegen_b200.synth import generate_kv
+    L, H, D, T = spec["num_layers"], spec["num_heads"], spec["head_size"], spec["num_tokens"]
+    ser, de, _, _ = make_serde(spec, 1, 0, chunk_size=T)
+    kv = generate_kv(L, H, D, T, spec["seed"], key_rho=spec["key_rho"], device=h.dev, dtype=torch.float16)
+    box = {}
+
+    def encode():
+        box["enc"] = ser.encode(kv)
+    encode()
+    ms_enc = h.timed(encode, 2, 1, local=True)
+    del kv
+    out = torch.empty((L, 2, T, H, D), dtype=torch.float16, device=h.dev)
+    plan = de.plan([box["enc"]], out=out, workspace={})
+    ms = h.timed(plan.run, max(3, args.steps // 2), 3, local=True)
+    de.check_status()
+    kv_bytes = 2 * L * H * D * T * 2
+    wire = plan.payload_bytes + plan.table_bytes + plan.length_bytes + plan.scale_bytes
+    return {"tokens": T, "serializer_calls": 1, "sub_chunks": len(box["enc"].data_chunks),
+            "value": kv_bytes / ms / 1e6, "unit": "GB/s", "ms_per_step": ms, "launches_per_step": plan.launches,
+            "encode_gbps": kv_bytes / ms_enc / 1e6, "encode_ms": ms_enc,
+            "bytes_per_token": wire / T,
+            "bytes_per_token_parts": {"payload": plan.payload_bytes / T, "tables": plan.table_bytes / T,
+                                      "lengths": plan.length_bytes / T, "scales": plan.scale_bytes / T}}
 
 
 def leg_config5(h, args):
@@ -867,6 +897,8 @@ def run_ours(args, spec):
             extra["anchor_delta"] = leg_anchor_delta(h, spec, generate_kv(L, H, D, 4 * CHUNK_TOKENS, spec["seed"],
                                                                        key_rho=spec["key_rho"], device=dev,
                                                                        dtype=torch.float16))
+            torch.cuda.empty_cache()
+            extra["whole_context_call"] = leg_whole_context(h, spec, args)
             torch.cuda.empty_cache()
             extra["config3"] = leg_config3(h, args)
             torch.cuda.empty_cache()

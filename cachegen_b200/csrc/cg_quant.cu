@@ -22,8 +22,7 @@ __device__ __forceinline__ uint32_t absmax2(uint32_t best, uint32_t packed) {
 }
 
 // One warp per (row, token).  scales[row, token] gets the 16-bit pattern of max|x|.
-// Rows row0 .. row0 + nrows - 1 (the host walks the rows in windows small enough for L2, so that the
-// quantise pass that follows a window finds its KV there).
+// Rows row0 .. row0 + nrows - 1.
 template <int VEC>
 __global__ void __launch_bounds__(256) row_absmax_kernel(const uint16_t *__restrict__ kv, const KvLayout L,
                                                          uint16_t *__restrict__ scales, int row0, int nrows) {

@@ -239,6 +239,31 @@ def test_encode_many_equals_chunk_by_chunk_encode(chunk_tokens):
     assert torch.equal(de.decode_many(many), want)
 
 
+@pytest.mark.parametrize("streams,batch", [(1, 1), (2, 3), (3, 16), (4, 2)])
+def test_encode_many_on_side_streams_gives_the_same_chunks(streams, batch):
+    """Consecutive chunks go to side streams in turn; the caller's stream -- here not the default one, with
+    the cache produced on it just before the call -- waits for them, so the chunks can be used at once."""
+    from cachegen_b200.synth import generate_kv
+    T = 256 * 6 + 40
+    base = generate_kv(32, 2, 128, T, seed=12, device="cuda", dtype=torch.float16)
+    ser, de = make_serde(256, "vllm", out_dtype=torch.float16)
+    want = [ser.encode(base[:, :, s:s + 256]) for s in range(0, T, 256)]
+    want_kv = de.decode_many(want)
+    torch.cuda.synchronize()
+    caller = torch.cuda.Stream()
+    with torch.cuda.stream(caller):
+        kv = base * 1.0  # made on the caller's stream: the side streams must wait for it
+        many = ser.encode_many(kv, batch=batch, streams=streams)
+        got_kv = de.decode_many(many)
+    caller.synchronize()
+    assert len(many) == len(want)
+    for a, b in zip(many, want):
+        assert torch.equal(a.cdf, b.cdf) and torch.equal(a.max_tensors_key, b.max_tensors_key)
+        assert torch.equal(a.data_chunks[0].bytestream, b.data_chunks[0].bytestream)
+        assert torch.equal(a.data_chunks[0].bytestream_lengths, b.data_chunks[0].bytestream_lengths)
+    assert torch.equal(got_kv, want_kv)
+
+
 def test_layer_shard_encodes_like_the_whole_model():
     """Layers 20..29 of the 70B configuration have 32 key bins and 16 value bins.  Encoded as a shard
     with the whole model's table length they give exactly the whole model's tables, lengths and
