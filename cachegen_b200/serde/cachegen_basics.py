@@ -436,9 +436,6 @@ def _load_storage_fast(b):
     return torch.storage.TypedStorage(wrap_storage=raw.untyped_storage(), dtype=dtype, _internal=True)
 
 
-_STAGE_PIECE = 4 << 20  # bytes copied into the staging memory between two host-to-device copies
-
-
 class _Staging:
     """Pinned host memory that a thread's blob loads and dumps pass through: bytes are copied into it
     by torch's multi-threaded CPU copy and leave it by an asynchronous copy on the current stream
@@ -477,12 +474,9 @@ class _Staging:
             return view_cpu.to(device)  # no load in progress, or more data than the blob announced
         stage = self.buf[self.pos:self.pos + n]
         self.pos += (n + 255) // 256 * 256
+        stage.copy_(view_cpu)
         out = torch.empty(n, dtype=torch.uint8, device=device)
-        # in pieces, so that a piece is on its way to the GPU while the next is copied into the staging memory
-        for lo in range(0, n, _STAGE_PIECE):
-            hi = min(lo + _STAGE_PIECE, n)
-            stage[lo:hi].copy_(view_cpu[lo:hi])
-            out[lo:hi].copy_(stage[lo:hi], non_blocking=True)
+        out.copy_(stage, non_blocking=True)
         self.events[self.turn] = torch.cuda.Event()
         self.events[self.turn].record(torch.cuda.current_stream(device))
         return out
