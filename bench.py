@@ -664,6 +664,9 @@ def run_ours(args, spec):
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        # torchrun sets OMP_NUM_THREADS=1; the blob legs' host copies are torch's multi-threaded copies,
+        # so every rank gets its share of the host's cores, as a single process gets all of them
+        torch.set_num_threads(max(1, (os.cpu_count() or 1) // world))
     h = Harness(dev, rank, world)
     barrier, timed = h.barrier, h.timed
 
