@@ -19,12 +19,14 @@ standing in for real model KV.
   reference_cuda_ext  the reference's own CUDA extension (oracle/_ref, built unmodified) and the torch chain
                around it, on one 256-token chunk of the workload on this GPU, beside this package's kernels
   config3 / config5   the long-context GQA decode and a shortened three-quality-level encode + decode sweep
+  whole_context_call  the workload through one serializer call over all its tokens
 
 With N > 1 (under torchrun) every rank decodes its own request of the same shape (weak scaling, no
 data-path collective); the time is the max over ranks and the value the sum of all ranks' bytes.  The
 same run then measures, in the same process group, `h2d_only_ms` (the end-to-end leg's host-to-device
 copies alone) and `delivered_kv`: the Llama-70B-shape cache sharded by layers, every rank decoding its
-layers and the decoded KV delivered to GPU 0 over NVLink (pipelined copies, and NCCL after the decode).
+layers and the decoded KV delivered to GPU 0 over NVLink (pipelined copies, and NCCL after the decode),
+and `token_sharded`: one long-context request of the Mistral-7B GQA shape sharded by token chunks.
 `--impl reference` times the CPU restatement of the reference's decode path on the host cores.
 """
 import argparse
@@ -643,6 +645,52 @@ def leg_delivered_kv(h, args):
     return res
 
 
+def leg_token_sharded(h, args):
+    """BASELINE config 3 on the GPUs of the --gpus N run: ONE request of the Mistral-7B GQA shape (32 layers
+    x 8 KV heads x 128, 32,768 tokens = 128 chunks) sharded by token chunks -- every rank decodes a
+    contiguous run of the chunks -- with the decoded KV delivered into that token range of one blob on GPU 0
+    by pipelined peer copies.  Rank 0 also decodes the whole request alone and compares the delivered blob
+    bit for bit."""
+    torch = h.torch
+    from cachegen_b200.parallel import PipelinedDelivery, buffer_on_root, partition
+    from cachegen_b200.synth import WORKLOADS, generate_kv
+    spec = dict(WORKLOADS["mistral7b-gqa-32k"])
+    L, H, D, T = spec["num_layers"], spec["num_heads"], spec["head_size"], spec["num_tokens"]
+    nchunks = (T + CHUNK_TOKENS - 1) // CHUNK_TOKENS
+    mine = partition(nchunks, h.world, h.rank)
+    t0, t1 = mine.start * CHUNK_TOKENS, min(mine.stop * CHUNK_TOKENS, T)
+    ser, de, _, _ = make_serde(spec, h.world, h.rank)
+    # the generator's recurrence runs along the tokens: every rank makes the request and keeps its range
+    kv = generate_kv(L, H, D, T, spec["seed"], key_rho=spec["key_rho"], device=h.dev, dtype=torch.float16)
+    chunks = ser.encode_many(kv[:, :, t0:t1], CHUNK_TOKENS, batch=16)
+    want = None
+    if h.rank == 0:
+        want = de.decode_many(ser.encode_many(kv, CHUNK_TOKENS, batch=16))
+        de.check_status()
+    del kv
+    local = torch.empty((L, 2, t1 - t0, H, D), dtype=torch.float16, device=h.dev)
+    plan = de.plan(chunks, out=local, workspace={})
+    steps, warm = max(3, args.steps // 2), 2
+    total_bytes = 2 * L * H * D * T * 2
+    ms_decode = h.timed(plan.run, steps, warm)
+    shared = buffer_on_root((L, 2, T, H, D), torch.float16, root=0)
+    pipe = PipelinedDelivery(de, chunks, local, shared[:, :, t0:t1], parts=args.parts, target_is_local=(h.rank == 0))
+    ms_copy = h.timed(pipe.run, steps, warm)
+    ok_status = pipe.status() == 0
+    h.barrier()
+    same = bool(torch.equal(shared, want)) if h.rank == 0 else True
+    de.check_status()
+    return {"workload": "mistral7b-gqa-32k", "tokens": T, "chunks_per_gpu": len(mine), "kv_bytes": total_bytes,
+            "decode_only": {"ms_per_step": ms_decode, "value": total_bytes / ms_decode / 1e6, "unit": "GB/s",
+                            "tokens_per_s": T / ms_decode * 1e3,
+                            "what": "every rank decodes its run of chunks into its own memory; slowest rank"},
+            "pipelined_copy": {"ms_per_step": ms_copy, "gbps_into_gpu0": total_bytes / ms_copy / 1e6,
+                               "tokens_per_s": T / ms_copy * 1e3, "parts": len(pipe.parts),
+                               "what": "decode in parts; each part's token range goes into GPU 0's blob by peer "
+                                       "copies on a second stream while the next part is decoded"},
+            "delivered_bits_equal": same and ok_status, "scaling": "strong"}
+
+
 def run_ours(args, spec):
     import torch
     import torch.distributed as dist
@@ -910,6 +958,8 @@ def run_ours(args, spec):
             del chunks
             torch.cuda.empty_cache()
             extra["delivered_kv"] = leg_delivered_kv(h, args)
+            torch.cuda.empty_cache()
+            extra["token_sharded"] = leg_token_sharded(h, args)
 
     if rank != 0:
         if world > 1:
