@@ -264,6 +264,45 @@ def test_encode_many_on_side_streams_gives_the_same_chunks(streams, batch):
     assert torch.equal(got_kv, want_kv)
 
 
+@pytest.mark.parametrize("L,T", [(32, 256 * 8 + 100), (4, 8192)])
+def test_whole_context_call_decodes_to_the_values_of_chunked_calls(oracle, L, T):
+    """One serializer call over the whole context (chunk_size = context length, as the reference's
+    evaluation scripts call it: one table per stream group over all tokens, one stream per 256-token
+    sub-chunk).  Quantisation is per token row, so the decoded values cannot depend on how the context was
+    cut into calls: the result must equal the chunk-by-chunk result bit for bit; its tables and first
+    sub-chunk are checked against the oracle, and the blob goes through bytes and back."""
+    from cachegen_b200.synth import generate_kv
+    kv = generate_kv(L, 2, 128, T, seed=17, device="cuda", dtype=torch.float16)
+    # the 7B settings cover 32 layers; a shorter blob uses the first L of them, as the reference would
+    whole_ser, whole_de = make_serde(T, "vllm", out_dtype=torch.float16)
+    ser, de = make_serde(256, "vllm", out_dtype=torch.float16)
+    if L != 32:
+        from cachegen_b200.serde.cachegen_basics import CacheGenConfig
+        cfg = CacheGenConfig.from_model_name(MODEL_7B).layer_slice(0, L)
+        whole_ser, whole_de = make_serde(T, "vllm", out_dtype=torch.float16, cachegen_config=cfg)
+        ser, de = make_serde(256, "vllm", out_dtype=torch.float16, cachegen_config=cfg)
+    eo = whole_ser.encode(kv)
+    nsub = (T + 255) // 256
+    assert len(eo.data_chunks) == nsub and [c.ntokens for c in eo.data_chunks] == [min(256, T - 256 * j) for j in range(nsub)]
+    got = whole_de.decode(eo)
+    want = de.decode_many(ser.encode_many(kv))
+    whole_de.check_status()
+    de.check_status()
+    assert torch.equal(got, want)
+    assert torch.equal(whole_de.from_bytes(whole_ser.to_bytes(kv)), want)
+    # tables over all T tokens and the first sub-chunk's streams against the oracle (a few layers of it)
+    nl = min(L, 2)
+    from cachegen_b200.serde.cachegen_basics import make_key_bins, make_value_bins
+    kb = make_key_bins(whole_ser.cachegen_config, "cpu").numpy()[:nl]
+    vb = make_value_bins(whole_ser.cachegen_config, "cpu").numpy()[:nl]
+    ref = oracle_encode(oracle, kv[:nl].cpu(), kb, vb, oracle.F16)
+    rows = list(range(nl)) + list(range(L, L + nl))
+    if int(max(kb.max(), vb.max())) == eo.cdf.shape[2] - 1:
+        assert (eo.cdf[rows].cpu().numpy() == ref["cdf"]).all()
+        want_bytes, want_len = ref["chunks"][0]
+        assert (eo.data_chunks[0].bytestream_lengths[rows].cpu().numpy() == want_len).all()
+
+
 def test_layer_shard_encodes_like_the_whole_model():
     """Layers 20..29 of the 70B configuration have 32 key bins and 16 value bins.  Encoded as a shard
     with the whole model's table length they give exactly the whole model's tables, lengths and
