@@ -38,12 +38,21 @@ CG_HD int cg_clz(uint32_t x) {
     return x ? __builtin_clz(x) : 32;
 #endif
 }
-// x << n, 0 for n >= 32 (what the device's shift instruction gives)
+// x << n, 0 for n >= 32.  On the device a clamping funnel shift: a plain `<<` by 32 or more is undefined
+// to the compiler, which may then emit the wrapping form.
 CG_HD uint32_t cg_shl(uint32_t x, uint32_t n) {
 #if defined(__CUDA_ARCH__)
-    return x << n;
+    return __funnelshift_lc(0u, x, n);
 #else
     return n >= 32u ? 0u : x << n;
+#endif
+}
+// x >> n, 0 for n >= 32
+CG_HD uint32_t cg_shr(uint32_t x, uint32_t n) {
+#if defined(__CUDA_ARCH__)
+    return __funnelshift_rc(x, 0u, n);
+#else
+    return n >= 32u ? 0u : x >> n;
 #endif
 }
 // upper 32 bits of (hi:lo) << (s & 31)
@@ -493,25 +502,33 @@ struct BitSink {
     uint32_t *row;    // 4-byte aligned scratch row of this stream
     uint32_t cap_w;   // words that fit in the row
     uint32_t nwords;  // words produced so far (may exceed cap_w: then nothing more is stored)
-    uint64_t acc;     // pending output bits, right-aligned
-    uint32_t nacc;    // number of bits in acc, < 64
+    uint32_t acc_hi, acc_lo;  // pending output bits, right-aligned in (acc_hi:acc_lo)
+    uint32_t nacc;            // number of bits pending, < 64
 
     CG_HD void init(uint8_t *p, int64_t stride) {
         row = reinterpret_cast<uint32_t *>(p);
         cap_w = static_cast<uint32_t>(stride >> 2);
         nwords = 0;
-        acc = 0;
+        acc_hi = 0;
+        acc_lo = 0;
         nacc = 0;
     }
-    // appends the low n bits of v (v has no bits above n); needs nacc + n <= 64
+    // appends the low n bits of v (v has no bits above n), n <= 32; needs nacc + n <= 64
     CG_HD void put(uint32_t v, uint32_t n) {
-        acc = (acc << n) | v;
+        acc_hi = cg_fshl_clamp(acc_lo, acc_hi, n);
+        acc_lo = cg_shl(acc_lo, n) | v;
+        nacc += n;
+    }
+    // the same for n < 32 (what the straight-line encoder step appends): plain funnel shifts
+    CG_HD void put_short(uint32_t v, uint32_t n) {
+        acc_hi = cg_fshl(acc_lo, acc_hi, n);
+        acc_lo = cg_shl(acc_lo, n) | v;
         nacc += n;
     }
     // moves the oldest 32 bits out; needs nacc >= 32
     CG_HD void store_word() {
         nacc -= 32u;
-        const uint32_t w = static_cast<uint32_t>(acc >> nacc);
+        const uint32_t w = cg_fshr_clamp(acc_lo, acc_hi, nacc);  // nacc < 32: the low word of (hi:lo) >> nacc
         if (nwords < cap_w) row[nwords] = cg_bswap32(w);
         nwords++;
     }
@@ -533,7 +550,7 @@ struct BitSink {
         drain();
         const uint32_t bytes = nwords * 4u + ((nacc + 7u) >> 3);
         if (nacc) {
-            const uint32_t w = static_cast<uint32_t>(acc << (32u - nacc));
+            const uint32_t w = acc_lo << (32u - nacc);  // after drain: 0 < nacc < 32
             if (nwords < cap_w) row[nwords] = cg_bswap32(w);
         }
         return bytes;
@@ -592,15 +609,15 @@ struct EncoderState {
     // goes ONE warp vote (see step), so that neither the repair nor the store is a per-lane branch in
     // the usual case.
     struct Before {
-        uint32_t low, span32, pending, nacc;
-        uint64_t acc;
+        uint32_t low, span32, pending, nacc, acc_hi, acc_lo;
     };
     CG_HD bool step_try(Smem sm, uint32_t col, uint32_t s, uint32_t maxsym, BitSink &out, Before &before) {
         before.low = low;
         before.span32 = span32;
         before.pending = pending;
         before.nacc = out.nacc;
-        before.acc = out.acc;
+        before.acc_hi = out.acc_hi;
+        before.acc_lo = out.acc_lo;
         const uint32_t a = col + s * kTableRowBytes;
         const uint32_t flo = cg_umulhi(span32, sm.ld(a));
         const uint32_t fnext = cg_umulhi(span32, sm.ld(a + kTableRowBytes));
@@ -608,24 +625,25 @@ struct EncoderState {
         low += flo;
         span32 = fhi - flo;
         const uint32_t high = low + span32 - 1u;
-        const uint32_t n1 = static_cast<uint32_t>(equal_shifts(low, high));
+        // low == high (32 here) and k == 32 below only come from a table that is not increasing: the first
+        // sends the lane to the general path (total > kFastEmitBits), the second makes the shifts give 0
+        const uint32_t n1 = static_cast<uint32_t>(cg_clz(low ^ high));
         const uint32_t y = cg_shl((~low) | high, n1);
-        const uint32_t k = static_cast<uint32_t>(cg_clz(y + y));  // 32 only on a table that is not increasing
+        const uint32_t k = static_cast<uint32_t>(cg_clz(y + y));
         // Output when n1 != 0: low's top bit, then the pending bits as its inverse, then low's next
-        // n1 - 1 bits.  Everything below is computed whatever n1 is (shift counts wrap or clamp) and
-        // masked off when there is nothing to put or the step has to be taken again.
-        const uint32_t total = n1 + pending;
-        const bool has = n1 != 0u;
-        const bool redo = (before.span32 == 0u) | (has & (total > kFastEmitBits));
-        const uint32_t keep = (has & !redo) ? 0xFFFFFFFFu : 0u;
-        const uint32_t first = low >> 31;
-        const uint32_t rest = cg_fshl(low + low, 0u, n1 - 1u);                 // the n1 - 1 bits after the first
-        const uint32_t head = ~cg_shl(0xFFFFFFFFu, pending) + first;            // first, then `pending` copies of its inverse
-        out.put((cg_shl(head, (n1 - 1u) & 31u) | rest) & keep, total & keep);
-        pending = (has ? 0u : pending) + k;
-        const uint32_t sh = (n1 + k) & 31u;
-        low = (low << sh) & 0x7FFFFFFFu;
-        span32 <<= sh;
+        // n1 - 1 bits.  As a number that is (2^q - 1) * 2^(n1 - 1) + (low's top n1 bits), q the pending
+        // count: the sum carries into the top bit's place exactly when that bit is 1.  With n1 == 0 nothing
+        // goes out: q is taken as 0 then, which makes the value 0 and the bit count 0 without a mask.  A
+        // lane that has to take the step again may append anything: step_finish puts its accumulator back.
+        const uint32_t q = n1 ? pending : 0u;
+        const uint32_t nput = n1 + q;
+        const bool redo = (before.span32 == 0u) | (nput > kFastEmitBits);
+        const uint32_t ones = cg_shl(1u, q) - 1u;
+        out.put_short(cg_shl(ones, n1 - 1u) + cg_fshl(low, 0u, n1), nput);
+        pending = pending - q + k;
+        const uint32_t sh = n1 + k;  // at most 18 with an increasing table
+        low = cg_shl(low, sh) & 0x7FFFFFFFu;
+        span32 = cg_shl(span32, sh);
         return redo;
     }
     CG_HD void step_finish(bool redo, const Before &before, Smem sm, uint32_t col, uint32_t s, uint32_t maxsym,
@@ -634,7 +652,8 @@ struct EncoderState {
             low = before.low;
             span32 = before.span32;
             pending = before.pending;
-            out.acc = before.acc;
+            out.acc_hi = before.acc_hi;
+            out.acc_lo = before.acc_lo;
             out.nacc = before.nacc;
             step_general(sm, col, s, maxsym, out);
         }

@@ -44,20 +44,28 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
     enc.init();
     uint32_t largest = 0;  // the largest symbol met: one above maxsym is reported and coded as maxsym
 
+    // whole groups of kPrefetch symbols: their loads are issued together, ahead of the coder, with no
+    // bound checks; the last, shorter group goes symbol by symbol
     const int64_t s1 = p.s1;
-    for (int base = 0; base < n; base += kPrefetch) {
+    const uint8_t *sp8 = reinterpret_cast<const uint8_t *>(sp);
+    const uint32_t top = static_cast<uint32_t>(maxsym);
+    int base = 0;
+    for (; base + kPrefetch <= n; base += kPrefetch) {
         uint32_t buf[kPrefetch];
 #pragma unroll
-        for (int j = 0; j < kPrefetch; ++j) {
-            buf[j] = (base + j < n) ? static_cast<uint8_t>(__ldg(sp)) : 0u;
-            sp += s1;
-        }
+        for (int j = 0; j < kPrefetch; ++j) buf[j] = __ldg(sp8 + j * s1);
+        sp8 += kPrefetch * s1;
 #pragma unroll
         for (int j = 0; j < kPrefetch; ++j) {
-            if (base + j >= n) break;
             largest = max(largest, buf[j]);
-            enc.step(Smem{}, col, min(buf[j], static_cast<uint32_t>(maxsym)), static_cast<uint32_t>(maxsym), out, lanes);
+            enc.step(Smem{}, col, min(buf[j], top), top, out, lanes);
         }
+    }
+    for (; base < n; ++base) {
+        const uint32_t s = __ldg(sp8);
+        sp8 += s1;
+        largest = max(largest, s);
+        enc.step(Smem{}, col, min(s, top), top, out, lanes);
     }
     const uint32_t nbytes = enc.flush(out);
     p.lengths[slot] = static_cast<int32_t>(nbytes);
