@@ -217,6 +217,15 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
         // histogram updates at different channels, so that the 32 lanes of a warp always hit 32
         // different banks of hist[.][channel]
         const int rot = (threadIdx.x & 31) >> 2;
+        // for the e-th update of a step: which of the step's eight symbols it counts (a byte selector
+        // for the packed pair of words) and the byte offset of that channel inside a histogram row
+        uint32_t pick[8], place[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            pick[e] = static_cast<uint32_t>((e + rot) & 7);
+            place[e] = static_cast<uint32_t>(q * 8 + ((e + rot) & 7)) * 4u;
+        }
+        const uint32_t top_bin = static_cast<uint32_t>(max_bins);
         if (c < C) {
             for (int t = tsub; t < T; t += kTokensPerStep) {
                 const uint16_t mbits = __ldg(srow + t);
@@ -244,22 +253,23 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_cdf_kernel(
                     }
                 }
                 const uint32_t up = resid ? shift : 0u;
-                uint64_t packed = 0;
+                uint32_t packed[2] = {0u, 0u};
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
                     const uint16_t hb = static_cast<uint16_t>(w[e >> 1] >> ((e & 1) * 16));
                     // three separately rounded fp32 operations, then round-half-even (enc.py:56-57)
                     const float p = __fmul_rn(Half16<DT>::to_float(hb), factor);
                     const float qv = __fadd_rn(p, mq);
-                    const uint32_t s = ((__float_as_uint(__fadd_rn(qv, 8388608.0f)) & keep) + up) & 0xFFu;
-                    packed |= static_cast<uint64_t>(s) << (8 * e);
+                    uint32_t s = __float_as_uint(__fadd_rn(qv, 8388608.0f)) & keep;
+                    if (DELTA) s = (s + up) & 0xFFu;
+                    packed[e >> 2] |= s << (8 * (e & 3));
                 }
-                *reinterpret_cast<uint64_t *>(orow + static_cast<int64_t>(t) * C + c) = packed;
+                *reinterpret_cast<uint2 *>(orow + static_cast<int64_t>(t) * C + c) = make_uint2(packed[0], packed[1]);
+                const char *hist_bytes = reinterpret_cast<const char *>(hist);
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    const int ee = (e + rot) & 7;
-                    const uint32_t s = static_cast<uint32_t>(packed >> (8 * ee)) & 0xFFu;
-                    atomicAdd(&hist[min(s, static_cast<uint32_t>(max_bins)) * kGroup + q * 8 + ee], 1u);
+                    const uint32_t s = __byte_perm(packed[0], packed[1], pick[e]) & 0xFFu;
+                    atomicAdd(reinterpret_cast<uint32_t *>(const_cast<char *>(hist_bytes) + min(s, top_bin) * (kGroup * 4u) + place[e]), 1u);
                 }
             }
         }
