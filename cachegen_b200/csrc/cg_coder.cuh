@@ -47,14 +47,6 @@ CG_HD uint32_t cg_shl(uint32_t x, uint32_t n) {
     return n >= 32u ? 0u : x << n;
 #endif
 }
-// x >> n, 0 for n >= 32
-CG_HD uint32_t cg_shr(uint32_t x, uint32_t n) {
-#if defined(__CUDA_ARCH__)
-    return __funnelshift_rc(x, 0u, n);
-#else
-    return n >= 32u ? 0u : x >> n;
-#endif
-}
 // upper 32 bits of (hi:lo) << (s & 31)
 CG_HD uint32_t cg_fshl(uint32_t lo, uint32_t hi, uint32_t s) {
 #if defined(__CUDA_ARCH__)
