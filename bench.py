@@ -834,7 +834,7 @@ def run_ours(args, spec):
 
         def measure_host(host_chunks, nbytes, what):
             def e2e_step():
-                de.decode_many_host(host_chunks, out=out, groups=16)
+                de.decode_many_host(host_chunks, out=out, groups=32)
                 status_host.copy_(de.group_status_words()[-1], non_blocking=True)
             ms = timed(e2e_step, max(2, args.steps // 2), 2)
             torch.cuda.synchronize()
@@ -858,7 +858,7 @@ def run_ours(args, spec):
         kv = None
         e2e = measure_host(flat_host, sum(c.header.total for c in flat_host),
                            "CacheGenDeserializer.decode_many_host on CGB2 containers (CacheGenSerializer.encode_flat) "
-                           "held in pinned host memory; 16 groups, copies of one group overlap the decode of the previous")
+                           "held in pinned host memory; 32 groups, copies of one group overlap the decode of the previous")
         # the same copies with no decode: what the bus alone takes (every rank copies at once)
         dev_flat = [torch.empty_like(c.blob, device=dev) for c in flat_host]
 

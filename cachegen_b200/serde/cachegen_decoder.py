@@ -491,10 +491,10 @@ class CacheGenDeserializer(Deserializer):
     def decode_many_host(self, encoder_outputs: List[CacheGenGPUEncoderOutput], out: torch.Tensor = None,
                          groups: int = None) -> torch.Tensor:
         """decode_many for chunks whose tensors sit in pinned host memory: copies and decodes overlap.
-        groups: how many parts the chunks are split into (default: up to 16); the decode of a part
+        groups: how many parts the chunks are split into (default: up to 32); the decode of a part
         runs while the next one is copied, so the last part's decode is all that is not hidden."""
         if groups is None:
-            groups = min(16, len(encoder_outputs))
+            groups = min(32, len(encoder_outputs))
         ws = self._workspace.setdefault("groups", [dict() for _ in range(groups)])
         if len(ws) < groups:
             ws += [dict() for _ in range(groups - len(ws))]
