@@ -514,7 +514,7 @@ struct BitSink {
     // the same for n < 32 (what the straight-line encoder step appends): plain funnel shifts
     CG_HD void put_short(uint32_t v, uint32_t n) {
         acc_hi = cg_fshl(acc_lo, acc_hi, n);
-        acc_lo = cg_shl(acc_lo, n) | v;
+        acc_lo = acc_lo * cg_shl(1u, n) + v;  // a multiply-add for shift and or: off the integer pipe, which binds the encoder
         nacc += n;
     }
     // moves the oldest 32 bits out; needs nacc >= 32
@@ -634,8 +634,9 @@ struct EncoderState {
         out.put_short(cg_shl(ones, n1 - 1u) + cg_fshl(low, 0u, n1), nput);
         pending = pending - q + k;
         const uint32_t sh = n1 + k;  // at most 18 with an increasing table
-        low = cg_shl(low, sh) & 0x7FFFFFFFu;
-        span32 = cg_shl(span32, sh);
+        const uint32_t p2 = cg_shl(1u, sh);  // one shift and two multiplies for two shifts: see put_short
+        low = (low * p2) & 0x7FFFFFFFu;
+        span32 = span32 * p2;
         return redo;
     }
     CG_HD void step_finish(bool redo, const Before &before, Smem sm, uint32_t col, uint32_t s, uint32_t maxsym,
