@@ -555,11 +555,19 @@ constexpr uint32_t kFastEmitBits = 16;   // ... so up to this many more fit with
 
 struct EncoderState {
     uint32_t low, span32, pending;  // span32 = (high - low + 1) mod 2^32, 0 for the full range
-    CG_HD void init() {
+    // 1 and -1 as values the compiler cannot see through (the kernel reads them from constant memory):
+    // a + b written as a * one + b is a multiply-add, which keeps it off the integer pipe that binds the
+    // encoder's step; a plain a + b would be folded back into an integer add
+    uint32_t one, minus_one;
+    CG_HD void init(uint32_t opaque_one = 1u, uint32_t opaque_minus_one = 0xFFFFFFFFu) {
         low = 0u;
         span32 = 0u;
         pending = 0u;
+        one = opaque_one;
+        minus_one = opaque_minus_one;
     }
+    CG_HD uint32_t add_f(uint32_t a, uint32_t b) const { return a * one + b; }
+    CG_HD uint32_t sub_f(uint32_t a, uint32_t b) const { return b * minus_one + a; }  // a - b
     // One symbol s in [0, maxsym] (enc_new.cu:257-295), any state, any number of output bits; stores
     // whole words as needed but leaves up to 63 bits in the accumulator.  The table column must have
     // a readable row after the last symbol's.
@@ -614,8 +622,8 @@ struct EncoderState {
         const uint32_t flo = cg_umulhi(span32, sm.ld(a));
         const uint32_t fnext = cg_umulhi(span32, sm.ld(a + kTableRowBytes));
         const uint32_t fhi = (s == maxsym) ? span32 : fnext;
-        low += flo;
-        span32 = fhi - flo;
+        low = add_f(low, flo);
+        span32 = sub_f(fhi, flo);
         const uint32_t high = low + span32 - 1u;
         // low == high (32 here) and k == 32 below only come from a table that is not increasing: the first
         // sends the lane to the general path (total > kFastEmitBits), the second makes the shifts give 0
@@ -628,12 +636,12 @@ struct EncoderState {
         // goes out: q is taken as 0 then, which makes the value 0 and the bit count 0 without a mask.  A
         // lane that has to take the step again may append anything: step_finish puts its accumulator back.
         const uint32_t q = n1 ? pending : 0u;
-        const uint32_t nput = n1 + q;
+        const uint32_t nput = add_f(n1, q);
         const bool redo = (before.span32 == 0u) | (nput > kFastEmitBits);
         const uint32_t ones = cg_shl(1u, q) - 1u;
         out.put_short(cg_shl(ones, n1 - 1u) + cg_fshl(low, 0u, n1), nput);
-        pending = pending - q + k;
-        const uint32_t sh = n1 + k;  // at most 18 with an increasing table
+        pending = add_f(sub_f(pending, q), k);
+        const uint32_t sh = add_f(n1, k);  // at most 18 with an increasing table
         const uint32_t p2 = cg_shl(1u, sh);  // one shift and two multiplies for two shifts: see put_short
         low = (low * p2) & 0x7FFFFFFFu;
         span32 = span32 * p2;

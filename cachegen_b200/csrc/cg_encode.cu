@@ -17,6 +17,10 @@ struct EncodeParams {
     int32_t *status;
 };
 
+// see EncoderState::add_f
+__constant__ uint32_t opaque_one = 1u;
+__constant__ uint32_t opaque_minus_one = 0xFFFFFFFFu;
+
 constexpr int kPrefetch = 8;  // symbols fetched ahead of the coder
 
 __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
@@ -41,7 +45,7 @@ __global__ void __launch_bounds__(kGroup) encode_kernel(const EncodeParams p) {
 
     const int8_t *sp = p.sym + row * p.s0 + static_cast<int64_t>(t0) * p.s1 + c * p.s2;
     EncoderState enc;
-    enc.init();
+    enc.init(opaque_one, opaque_minus_one);
     uint32_t largest = 0;  // the largest symbol met: one above maxsym is reported and coded as maxsym
 
     // whole groups of kPrefetch symbols: their loads are issued together, ahead of the coder, with no
